@@ -1,0 +1,219 @@
+/*
+ * zdraw_cuda.h — C ABI of the B200 (sm_100a) joint-attention path.
+ *
+ * This is the CUDA counterpart of the attention slice of the reference's Metal
+ * bridge ABI (src/metal/metal_c.zig; C side src/metal/metal_api.m). A host layer
+ * (Zig, C, C++ or ctypes) calls these functions where the reference's DiT blocks
+ * call `zdraw_metal_run_qk_norm_rope` / `zdraw_metal_run_attention*`.
+ *
+ * Conventions kept from the reference bridge:
+ *   - plain C functions, opaque context handle, `int` return:
+ *       0  = ok, work enqueued on the caller's stream
+ *       1  = declined: the shape is outside what the kernels take; nothing was
+ *            enqueued (metal_api.m:6604-6607, 6776-6777). There is no CPU fallback.
+ *       <0 = failure (bad argument, CUDA error)
+ *   - every tensor is a caller-owned DEVICE pointer, borrowed until the stream
+ *     reaches the end of the call; the library owns only its context scratch;
+ *   - work is enqueued on the caller's stream and the caller synchronises
+ *     (as with zdraw_metal_batch_begin/end, metal_api.m:1092-1113);
+ *   - a context is used by one host thread at a time;
+ *   - struct sizes are asserted on both sides (src/abi_gen.zig:20-57,
+ *     src/runtime/abi_assert.zig:25-41): see ZDRAW_CUDA_ATTN_PARAMS_SIZE.
+ *
+ * `stream` is a cudaStream_t passed as void* (NULL = the default stream).
+ */
+#ifndef ZDRAW_CUDA_H
+#define ZDRAW_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define ZDRAW_CUDA_API __attribute__((visibility("default")))
+#else
+#define ZDRAW_CUDA_API
+#endif
+
+#define ZDRAW_CUDA_OK 0
+#define ZDRAW_CUDA_DECLINED 1
+#define ZDRAW_CUDA_E_ARG (-1)    /* null/misaligned pointer, zero size, bad enum          */
+#define ZDRAW_CUDA_E_CUDA (-2)   /* a CUDA runtime/driver call failed                      */
+#define ZDRAW_CUDA_E_DEVICE (-3) /* a kernel gave up a bounded wait; see last_status       */
+
+/* Element type codes: the reference's dtype codes (src/metal/mres_util.zig:11-18). */
+#define ZDRAW_DTYPE_F16 1u
+#define ZDRAW_DTYPE_F32 3u
+
+/* Tensor layouts. D = head_dim is always innermost and contiguous. */
+#define ZDRAW_LAYOUT_TOKEN_MAJOR 0u /* [batch][tokens][heads][D], token stride ld_* elements */
+#define ZDRAW_LAYOUT_HEAD_MAJOR 1u  /* [batch][heads][tokens][D], dense                      */
+
+/* Attention kernels. 0 is the product kernel; 1 is a slow scalar kernel kept to
+ * cross-check it in tests (the reference keeps `attention_rows` beside its fast
+ * kernels the same way, src/metal/mattn_test.zig:91-128). */
+#define ZDRAW_KERNEL_TCGEN05 0u
+#define ZDRAW_KERNEL_SCALAR 1u
+
+/*
+ * Call descriptor. Mirrors AttnParams (src/metal/metal_c.zig:245-256: tokens,
+ * heads, kv_heads, head_dim, causal, valid) plus what QkNormParams
+ * (metal_c.zig:258-274) and the Klein glue kernels carry (eps, dtype, segment
+ * split). The DiT path always has kv_heads == heads, causal == 0
+ * (src/klein/zflux2_dit.zig:320-326), so those two fields are not repeated;
+ * `valid` is generalised to an additive per-key mask.
+ */
+typedef struct zdraw_cuda_attn_params {
+  uint32_t batch;        /* images (seeds); attention never crosses images            */
+  uint32_t tokens;       /* S per image                                               */
+  uint32_t heads;        /* H                                                         */
+  uint32_t head_dim;     /* must be 128, else the call is declined                    */
+  uint32_t txt_tokens;   /* rows [0,txt_tokens) use *_w_txt, the rest *_w_img         */
+  uint32_t in_dtype;     /* dtype of q,k,v given to the prologue / of v given to attention */
+  uint32_t out_dtype;    /* dtype of o                                                */
+  uint32_t out_layout;   /* ZDRAW_LAYOUT_* of o                                       */
+  uint32_t qk_layout;    /* layout of the fp16 q/k between prologue and attention     */
+  uint32_t has_key_mask; /* 0/1                                                       */
+  uint32_t kernel;       /* ZDRAW_KERNEL_*                                            */
+  uint32_t reserved;     /* must be 0                                                 */
+  float norm_eps;        /* 1e-6 Klein, 1e-5 Z-Image                                  */
+  float softmax_scale;   /* 0 => 1/sqrt(head_dim)                                     */
+  uint64_t ld_q, ld_k, ld_v, ld_o; /* token strides in elements; 0 => heads*head_dim.
+                                      Image b starts at b*tokens*ld (the reference's
+                                      batched layout, zflux2_resident.zig:1407-1411). */
+  uint64_t mask_batch_stride; /* elements between images in key_mask; 0 = one mask shared */
+  uint64_t rope_batch_stride; /* elements between images in rope_cos/sin; 0 = one table shared */
+} zdraw_cuda_attn_params;
+
+#define ZDRAW_CUDA_ATTN_PARAMS_SIZE 104
+#if defined(__cplusplus)
+static_assert(sizeof(zdraw_cuda_attn_params) == ZDRAW_CUDA_ATTN_PARAMS_SIZE, "ABI size");
+#else
+_Static_assert(sizeof(zdraw_cuda_attn_params) == ZDRAW_CUDA_ATTN_PARAMS_SIZE, "ABI size");
+#endif
+
+/* sizeof(zdraw_cuda_attn_params) as the library was compiled; a binding asserts
+ * it equals its own (the role of src/abi_gen.zig's generated size header). */
+ZDRAW_CUDA_API size_t zdraw_cuda_attn_params_size(void);
+
+/*
+ * Context create/destroy. Replaces mattn.Context.init / deinit
+ * (src/metal/mattn.zig:65-132): selects the device, allocates the status word,
+ * resolves the driver's tensor-map encoder. Scratch (fp16 q/k between prologue
+ * and attention, an fp16 copy of f32 v) is grow-only, like the reference's
+ * scratch slots (metal_api.m:6147-6191), and is sized by the first call that
+ * needs it or by zdraw_cuda_attn_reserve.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_attn_create(int device, void **ctx);
+ZDRAW_CUDA_API int zdraw_cuda_attn_destroy(void *ctx);
+
+/* Pre-sizes the context scratch for `p` so that later calls allocate nothing
+ * (zdraw_metal_attn_hm_scratch, metal_c.zig:322-326, plays this role). */
+ZDRAW_CUDA_API int zdraw_cuda_attn_reserve(void *ctx, const zdraw_cuda_attn_params *p);
+
+/*
+ * Prologue: per-(token, head) RMSNorm with per-segment weights, pair-rotation
+ * RoPE from per-token cos/sin tables, cast to fp16. Replaces
+ * zdraw_metal_run_qk_norm_rope (metal_c.zig:148-159, kernel
+ * src/metal/mqk_shader.zig:46-97, head-major variant metal_api.m:6201-6266) and
+ * the Klein kernels krms_rope / krms_rope_hm
+ * (src/klein/zflux2_glue_shader.zig:61-122, call sites
+ * src/klein/zflux2_resident.zig:1573-1669).
+ *   q, k        : in_dtype, token-major with ld_q / ld_k
+ *   *_w_*       : f32 [head_dim], one vector shared by every head
+ *   rope_cos/sin: f32 [tokens][head_dim], cos[t][2i] == cos[t][2i+1]
+ *   q_out,k_out : fp16 in qk_layout (token-major here is dense, ld = heads*head_dim)
+ */
+ZDRAW_CUDA_API int zdraw_cuda_qk_norm_rope(void *ctx, void *stream, const void *q, const void *k,
+                            const float *q_w_txt, const float *q_w_img, const float *k_w_txt,
+                            const float *k_w_img, const float *rope_cos, const float *rope_sin,
+                            void *q_out_f16, void *k_out_f16, const zdraw_cuda_attn_params *p);
+
+/*
+ * Non-causal attention on already normalised, rotated fp16 q/k. Replaces
+ * zdraw_metal_run_attention_steel_route_enc / _mfa_hm_enc / run_attention_enc
+ * (metal_c.zig:287-353; steel kernel vendor/steel attn_entry.metal:39-46).
+ *   q_f16,k_f16 : fp16 in qk_layout (token-major uses ld_q / ld_k)
+ *   v           : in_dtype, token-major with ld_v (f32 v is cast into context scratch)
+ *   key_mask    : f32 [tokens] additive per-key term (0 / -inf), or NULL
+ *   o           : out_dtype in out_layout (token-major uses ld_o, which may exceed
+ *                 heads*head_dim to write straight into a wider operand, as
+ *                 kunperm_hm_hh does, zflux2_glue_shader.zig:128-158)
+ */
+ZDRAW_CUDA_API int zdraw_cuda_attention(void *ctx, void *stream, const void *q_f16, const void *k_f16,
+                         const void *v, const float *key_mask, void *o,
+                         const zdraw_cuda_attn_params *p);
+
+/*
+ * Prologue + attention in one call: what a DiT block does with rmsRopeHm x2/x4
+ * followed by runAttnHm (zflux2_resident.zig:1544-1558, 2005-2017; Z-Image
+ * chain metal_api.m:7159-7183). The fp16 q/k live in context scratch.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_joint_attention(void *ctx, void *stream, const void *q, const void *k,
+                               const void *v, const float *q_w_txt, const float *q_w_img,
+                               const float *k_w_txt, const float *k_w_img,
+                               const float *rope_cos, const float *rope_sin,
+                               const float *key_mask, void *o, const zdraw_cuda_attn_params *p);
+
+/*
+ * The same with HOST buffers: uploads q, k, v (and tables, weights, mask), runs
+ * the joint path, reads o back and returns when it is on the host. Replaces the
+ * fresh-buffer route mattn.Context.run -> runFresh (src/metal/mattn.zig:152-173,
+ * 349-374). Device staging buffers are grow-only context scratch.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_joint_attention_host(void *ctx, const void *q, const void *k, const void *v,
+                                    const float *q_w_txt, const float *q_w_img,
+                                    const float *k_w_txt, const float *k_w_img,
+                                    const float *rope_cos, const float *rope_sin,
+                                    const float *key_mask, void *o,
+                                    const zdraw_cuda_attn_params *p);
+
+/*
+ * Attention alone with HOST buffers (no prologue): q, k, v in in_dtype, token-major;
+ * f32 q/k/v are cast to fp16 on the device first. This is the call shape of
+ * mattn.Context.run (src/metal/mattn.zig:152-173: out, q, k, v slices + Config),
+ * which the reference's GPU-vs-CPU tests use (src/metal/mattn_test.zig:8-128).
+ */
+ZDRAW_CUDA_API int zdraw_cuda_attention_host(void *ctx, const void *q, const void *k, const void *v,
+                                             const float *key_mask, void *o,
+                                             const zdraw_cuda_attn_params *p);
+
+/*
+ * Host-side RoPE tables in the per-token form the prologue takes.
+ * Klein: buildRopeRef (src/klein/zflux2_dit.zig:125-170), four 32-dim axes,
+ * ids text (0,0,0,l), image (0,row,col,0), reference image (10,row,col,0).
+ * cos/sin receive [txt_len + grid_h*grid_w + ref_h*ref_w][128] f32 (host memory).
+ */
+ZDRAW_CUDA_API int zdraw_cuda_klein_rope_table(float *cos_out, float *sin_out, size_t txt_len, size_t grid_h,
+                                size_t grid_w, size_t ref_h, size_t ref_w, double theta);
+
+/*
+ * Z-Image: zrope.Cache.init + per-token gather (src/zimage/zrope.zig:32-38,
+ * 88-116) for the unified sequence [image | caption] with positions image
+ * (cap_total+1, r, c) and caption (1+i, 0, 0) (src/zimage/zunify.zig:16-37,
+ * zstep_shape.zig:58-66). dims/lens are the three axis sizes (sum(dims) == 128).
+ * Returns -1 for a configuration or position the reference rejects
+ * (InvalidConfig / BadPosition).
+ */
+ZDRAW_CUDA_API int zdraw_cuda_zimage_rope_table(float *cos_out, float *sin_out, size_t img_h, size_t img_w,
+                                 size_t cap_total, const size_t dims[3], const size_t lens[3],
+                                 float theta);
+
+/*
+ * Reads (and clears) the device status word. 0 = every kernel ran to the end.
+ * Non-zero = a kernel gave up a bounded wait and returned early; the output of
+ * that call is invalid. Synchronises `stream`. Plays the part of the bridge's
+ * per-route fallback counters (metal_api.m:350, 459, 6785).
+ */
+ZDRAW_CUDA_API int zdraw_cuda_last_status(void *ctx, void *stream, uint32_t *device_status);
+
+/* Human-readable text of the last failure on this context (never NULL). */
+ZDRAW_CUDA_API const char *zdraw_cuda_last_error(void *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZDRAW_CUDA_H */

@@ -1,0 +1,199 @@
+"""Attention parity on the GPU, through the C ABI, against the CPU oracle.
+
+Follows the reference's three tiers (src/metal/mattn_test.zig): known answers, a ragged shape
+matrix at the reference's tolerances, then full-size runs checked on sampled rows with
+byte-identical repeats.
+"""
+import numpy as np
+import pytest
+
+from zdraw_b200 import _lib, mattn, workloads
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+# fp16 I/O acceptance: max-abs <= 1e-2 and mean-abs <= 1e-3 against the fp32 oracle.
+MAX_ABS, MEAN_ABS = 1e-2, 1e-3
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device; none is visible (not a pass)")
+    _lib.build()
+    c = mattn.Context(0)
+    yield c
+    assert c.last_status() == 0
+    c.deinit()
+
+
+def embed(values, tokens, heads, dim):
+    """Known-answer vectors have head_dim 1 or 2; the kernels take 128: pad with zeros."""
+    a = np.zeros((tokens, heads, 128), np.float32)
+    a[:, :, :dim] = np.asarray(values, np.float32).reshape(tokens, heads, dim)
+    return a
+
+
+# ----------------------------------------------------------------------------- tier 1
+def test_known_answer_single_token_returns_value(ctx):
+    # attention.zig:115-123 (head_dim 2 padded to 128; scale set for head_dim 2 does not matter for one key).
+    q, k, v = embed([1, 0], 1, 1, 2), embed([1, 0], 1, 1, 2), embed([3, 4], 1, 1, 2)
+    out = np.full_like(q, np.nan)
+    ctx.run(out, q, k, v, mattn.Config(1, 1, 1, 128))
+    assert abs(out[0, 0, 0] - 3.0) <= 1e-3 and abs(out[0, 0, 1] - 4.0) <= 1e-3
+    assert not out[0, 0, 2:].any()
+
+
+def test_known_answer_padding_limit(ctx, oracle):
+    # attention.zig:135-156 without the causal part: valid=2 of 3 keys; every row averages v[0], v[1].
+    q, k, v = embed([1, 1, 1], 3, 1, 1), embed([0, 0, 100], 3, 1, 1), embed([1, 2, 99], 3, 1, 1)
+    out = np.full_like(q, np.nan)
+    ctx.run(out, q, k, v, mattn.Config(3, 1, 1, 128, valid=2))
+    np.testing.assert_allclose(out[:, 0, 0], [1.5, 1.5, 1.5], atol=1e-3)
+    open_out = np.full_like(q, np.nan)
+    ctx.run(open_out, q, k, v, mattn.Config(3, 1, 1, 128))
+    want = oracle.sdpa(q, k, v, 1)
+    np.testing.assert_allclose(open_out, want, atol=2e-3)
+    assert abs(open_out[2, 0, 0] - 99.0) <= 0.1  # the huge key dominates without the limit
+
+
+def test_known_answer_two_tokens_identity(ctx, oracle):
+    # mattn_test.zig:15-31 padded to head_dim 128.
+    q = embed([1, 0, 0, 1], 2, 1, 2)
+    v = embed([2, 4, 6, 8], 2, 1, 2)
+    out = np.full_like(q, np.nan)
+    ctx.run(out, q, q.copy(), v, mattn.Config(2, 1, 1, 128))
+    np.testing.assert_allclose(out, oracle.sdpa(q, q, v, 1), atol=1e-3)
+
+
+def test_unsupported_shapes_are_declined_not_emulated(ctx):
+    # The reference's small-head_dim known answers cannot run on this kernel: declined, no fallback.
+    x = np.zeros((2, 1, 2), np.float32)
+    with pytest.raises(mattn.UnsupportedShape):
+        ctx.run(np.zeros_like(x), x, x, x, mattn.Config(2, 1, 1, 2))
+    y = np.zeros((4, 2, 128), np.float32)
+    with pytest.raises(mattn.UnsupportedShape):
+        ctx.run(np.zeros_like(y), y, y, y, mattn.Config(4, 2, 2, 128, causal=True))
+    with pytest.raises(mattn.UnsupportedShape):
+        ctx.run(np.zeros_like(y), y, y[:, :1], y[:, :1], mattn.Config(4, 2, 1, 128))
+    with pytest.raises(mattn.InvalidShape):
+        ctx.run(np.zeros_like(y), y, y, y, mattn.Config(5, 2, 2, 128))
+
+
+# ----------------------------------------------------------------------------- tier 2
+BLOCK_CASES = [(16, 1), (48, 2), (53, 3), (288, 4), (289, 2)]           # mattn_test.zig:47-53
+EXTRA_CASES = [(32, 1), (80, 2), (257, 2), (128, 1), (129, 3), (384, 2), (640, 1)]
+
+
+@pytest.mark.parametrize("tokens,heads", BLOCK_CASES + EXTRA_CASES)
+def test_shape_matrix_matches_cpu(ctx, oracle, tokens, heads):
+    # Inputs N(0,1) * 0.5 and tolerance 2e-3: the reference's half-input kernel test (mattn_test.zig:66-88).
+    rng = np.random.default_rng(tokens * 31 + heads)
+    q, k, v = (rng.standard_normal((tokens, heads, 128)).astype(np.float32) * 0.5 for _ in range(3))
+    want = oracle.sdpa(q, k, v, heads)
+    got = np.full_like(q, np.nan)
+    ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128))
+    assert not np.isnan(got).any()
+    assert np.abs(got - want).max() <= 2e-3
+    # The scalar kernel on the same inputs agrees with both.
+    ref = np.full_like(q, np.nan)
+    ctx.run(ref, q, k, v, mattn.Config(tokens, heads, heads, 128), kernel=_lib.KERNEL_SCALAR)
+    assert np.abs(ref - want).max() <= 2e-3
+    assert np.abs(ref - got).max() <= 2e-3
+
+
+@pytest.mark.parametrize("tokens,heads", [(53, 2), (289, 3), (640, 2)])
+def test_unit_variance_inputs_and_f16_io(ctx, oracle, tokens, heads):
+    rng = np.random.default_rng(tokens)
+    q, k, v = (rng.standard_normal((tokens, heads, 128)).astype(np.float16) for _ in range(3))
+    want = oracle.sdpa(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32), heads)
+    got = np.full(q.shape, np.nan, np.float16)
+    ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128))
+    err = np.abs(got.astype(np.float32) - want)
+    assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS
+
+
+@pytest.mark.parametrize("tokens,masked", [(80, [(10, 20)]), (289, [(0, 128)]), (640, [(100, 400), (639, 640)]),
+                                          (384, [(128, 256)]), (200, [(150, 200)])])
+def test_key_mask(ctx, oracle, tokens, masked):
+    heads = 2
+    rng = np.random.default_rng(tokens + 7)
+    q, k, v = (rng.standard_normal((tokens, heads, 128)).astype(np.float32) * 0.5 for _ in range(3))
+    mask = np.zeros(tokens, np.float32)
+    for a, b in masked:
+        mask[a:b] = -np.inf
+    want = oracle.sdpa(q, k, v, heads, key_mask=mask)
+    for kernel in (_lib.KERNEL_TCGEN05, _lib.KERNEL_SCALAR):
+        got = np.full_like(q, np.nan)
+        ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128), key_mask=mask, kernel=kernel)
+        assert np.abs(got - want).max() <= 2e-3, f"kernel {kernel}"
+
+
+def test_finite_additive_mask_and_fully_masked(ctx, oracle):
+    tokens, heads = 160, 1
+    rng = np.random.default_rng(3)
+    q, k, v = (rng.standard_normal((tokens, heads, 128)).astype(np.float32) * 0.5 for _ in range(3))
+    mask = rng.uniform(-2.0, 0.0, tokens).astype(np.float32)
+    want = oracle.sdpa(q, k, v, heads, key_mask=mask)
+    got = np.full_like(q, np.nan)
+    ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128), key_mask=mask)
+    assert np.abs(got - want).max() <= 2e-3
+    # Every key masked: rows are written as zeros (the reference's math would give NaN).
+    got = np.full_like(q, np.nan)
+    ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128), key_mask=np.full(tokens, -np.inf, np.float32))
+    assert not got.any()
+
+
+@pytest.mark.parametrize("out_layout", [0, 1])
+@pytest.mark.parametrize("qk_layout", [0, 1])
+def test_device_call_layouts_and_strides(ctx, oracle, out_layout, qk_layout):
+    """run_on_handles: both q/k layouts, both O layouts, a wide O row stride, batch of 2, f16 out."""
+    batch, tokens, heads = 2, 200, 3
+    rng = np.random.default_rng(11)
+    q, k, v = (rng.standard_normal((batch, tokens, heads, 128)).astype(np.float16) for _ in range(3))
+    ld_o = heads * 128 + 256
+    dev = "cuda"
+    tq, tk = torch.from_numpy(q).to(dev), torch.from_numpy(k).to(dev)
+    if qk_layout == 1:
+        tq, tk = tq.permute(0, 2, 1, 3).contiguous(), tk.permute(0, 2, 1, 3).contiguous()
+    tv = torch.from_numpy(v).to(dev)
+    if out_layout == 0:
+        to = torch.full((batch, tokens, ld_o), float("nan"), dtype=torch.float16, device=dev)
+    else:
+        to = torch.full((batch, heads, tokens, 128), float("nan"), dtype=torch.float16, device=dev)
+    p = _lib.AttnParams(batch=batch, tokens=tokens, heads=heads, head_dim=128, in_dtype=1, out_dtype=1,
+                        out_layout=out_layout, qk_layout=qk_layout, ld_o=ld_o)
+    ctx.run_on_handles(tq, tk, tv, to, p)
+    torch.cuda.synchronize()
+    assert ctx.last_status() == 0
+    o = to.float().cpu().numpy()
+    for b in range(batch):
+        want = oracle.sdpa(q[b].astype(np.float32), k[b].astype(np.float32), v[b].astype(np.float32), heads)
+        if out_layout == 0:
+            got = o[b, :, :heads * 128].reshape(tokens, heads, 128)
+            assert np.isnan(o[b, :, heads * 128:]).all(), "wrote outside its columns"
+        else:
+            got = o[b].transpose(1, 0, 2)
+        err = np.abs(got - want)
+        assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS
+
+
+# ----------------------------------------------------------------------------- joint path, tiny config
+def test_joint_tiny_config_f32(ctx, oracle):
+    w = workloads.WORKLOADS["tiny"]
+    x = workloads.make_inputs(w, "cuda")
+    p = workloads.params(w)
+    out = torch.full((1, w.tokens, w.heads, 128), float("nan"), dtype=torch.float32, device="cuda")
+    ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                        x["rope_cos"], x["rope_sin"], out, p)
+    torch.cuda.synchronize()
+    h = {k: (v.cpu().numpy() if v is not None else None) for k, v in x.items()}
+    want = oracle.joint_attention(h["q"][0], h["k"][0], h["v"][0], h["q_w_txt"], h["q_w_img"], h["k_w_txt"],
+                                  h["k_w_img"], h["rope_cos"], h["rope_sin"], w.heads, w.txt_tokens, 0, w.eps)
+    err = np.abs(out[0].cpu().numpy() - want)
+    assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS
+    # Host-buffer entry point gives the same bytes as the device entry point.
+    out_h = np.full((1, w.tokens, w.heads, 128), np.nan, np.float32)
+    ctx.joint_attention_host(h["q"], h["k"], h["v"], h["q_w_txt"], h["q_w_img"], h["k_w_txt"], h["k_w_img"],
+                             h["rope_cos"], h["rope_sin"], out_h, p)
+    assert np.array_equal(out_h, out.cpu().numpy())

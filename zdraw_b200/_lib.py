@@ -1,0 +1,96 @@
+"""ctypes binding of ``libzdraw_cuda.so`` (the C ABI declared in ``include/zdraw_cuda.h``).
+
+The library is built in-tree by ``zdraw_b200/csrc/Makefile``. There is no fallback:
+if the shared library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libzdraw_cuda.so")
+CSRC_DIR = os.path.join(_HERE, "csrc")
+
+OK, DECLINED, E_ARG, E_CUDA, E_DEVICE = 0, 1, -1, -2, -3
+DTYPE_F16, DTYPE_F32 = 1, 3
+LAYOUT_TOKEN_MAJOR, LAYOUT_HEAD_MAJOR = 0, 1
+KERNEL_TCGEN05, KERNEL_SCALAR = 0, 1
+HEAD_DIM = 128
+
+
+class AttnParams(C.Structure):
+    """``zdraw_cuda_attn_params`` (include/zdraw_cuda.h); 104 bytes."""
+
+    _fields_ = [
+        ("batch", C.c_uint32),
+        ("tokens", C.c_uint32),
+        ("heads", C.c_uint32),
+        ("head_dim", C.c_uint32),
+        ("txt_tokens", C.c_uint32),
+        ("in_dtype", C.c_uint32),
+        ("out_dtype", C.c_uint32),
+        ("out_layout", C.c_uint32),
+        ("qk_layout", C.c_uint32),
+        ("has_key_mask", C.c_uint32),
+        ("kernel", C.c_uint32),
+        ("reserved", C.c_uint32),
+        ("norm_eps", C.c_float),
+        ("softmax_scale", C.c_float),
+        ("ld_q", C.c_uint64),
+        ("ld_k", C.c_uint64),
+        ("ld_v", C.c_uint64),
+        ("ld_o", C.c_uint64),
+        ("mask_batch_stride", C.c_uint64),
+        ("rope_batch_stride", C.c_uint64),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/zdraw_cuda.h declares.
+_VP, _PP = C.c_void_p, C.POINTER(AttnParams)
+SYMBOLS = {
+    "zdraw_cuda_attn_params_size": (C.c_size_t, []),
+    "zdraw_cuda_attn_create": (C.c_int, [C.c_int, C.POINTER(C.c_void_p)]),
+    "zdraw_cuda_attn_destroy": (C.c_int, [_VP]),
+    "zdraw_cuda_attn_reserve": (C.c_int, [_VP, _PP]),
+    "zdraw_cuda_qk_norm_rope": (C.c_int, [_VP] * 12 + [_PP]),
+    "zdraw_cuda_attention": (C.c_int, [_VP] * 7 + [_PP]),
+    "zdraw_cuda_joint_attention": (C.c_int, [_VP] * 13 + [_PP]),
+    "zdraw_cuda_joint_attention_host": (C.c_int, [_VP] * 12 + [_PP]),
+    "zdraw_cuda_attention_host": (C.c_int, [_VP] * 6 + [_PP]),
+    "zdraw_cuda_klein_rope_table": (C.c_int, [_VP, _VP] + [C.c_size_t] * 5 + [C.c_double]),
+    "zdraw_cuda_zimage_rope_table": (C.c_int, [_VP, _VP] + [C.c_size_t] * 3 + [_VP, _VP, C.c_float]),
+    "zdraw_cuda_last_status": (C.c_int, [_VP, _VP, C.POINTER(C.c_uint32)]),
+    "zdraw_cuda_last_error": (C.c_char_p, [_VP]),
+}
+
+_lib = None
+
+
+def build(verbose: bool = False) -> str:
+    """Compile the library for sm_100a with the Makefile in ``csrc/`` (nvcc; no GPU needed)."""
+    res = subprocess.run(["make", "-C", CSRC_DIR], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("building libzdraw_cuda.so failed:\n" + res.stdout + res.stderr)
+    if verbose:
+        print(res.stdout)
+    return LIB_PATH
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `make -C {CSRC_DIR}` "
+                "(there is no CPU or PyTorch fallback for this path)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (restype, argtypes) in SYMBOLS.items():
+            fn = getattr(handle, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        if handle.zdraw_cuda_attn_params_size() != C.sizeof(AttnParams):
+            raise RuntimeError("ABI mismatch: sizeof(zdraw_cuda_attn_params) differs between library and binding")
+        _lib = handle
+    return _lib

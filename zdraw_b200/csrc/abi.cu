@@ -1,0 +1,623 @@
+// extern "C" shim of the joint-attention path: argument validation, context scratch,
+// tensor-map construction and kernel launches. See include/zdraw_cuda.h for the contract
+// and for the reference entry points each function replaces.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../../include/zdraw_cuda.h"
+#include "attention_fwd.cuh"
+#include "prologue.cuh"
+
+namespace {
+
+using zdraw::AttnArgs;
+using zdraw::PrologueArgs;
+using zdraw::ScalarArgs;
+
+constexpr int kHeadDim = 128;
+constexpr uint32_t kMaxTokens = 1u << 20;
+constexpr float kLog2e = 1.4426950408889634f;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+struct Buf {
+  void* p = nullptr;
+  size_t cap = 0;
+};
+
+struct Ctx {
+  uint32_t magic = 0x5a444154u;  // "ZDAT"
+  int device = 0;
+  uint32_t* d_status = nullptr;
+  EncodeTiledFn encode = nullptr;
+  cudaStream_t host_stream = nullptr;  // used by the host-buffer entry point only
+  // Grow-only scratch (device memory).
+  Buf q16, k16, v16, tile_list;
+  Buf st_q, st_k, st_v, st_o, st_w, st_cos, st_sin, st_mask;  // staging for the host-buffer path
+  char err[256] = {0};
+};
+
+int fail(Ctx* c, int code, const char* fmt, ...) {
+  if (c) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(c->err, sizeof(c->err), fmt, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+#define ZD_CUDA(c, expr)                                                                      \
+  do {                                                                                        \
+    cudaError_t e_ = (expr);                                                                  \
+    if (e_ != cudaSuccess) return fail((c), ZDRAW_CUDA_E_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+Ctx* as_ctx(void* p) {
+  Ctx* c = static_cast<Ctx*>(p);
+  return (c && c->magic == 0x5a444154u) ? c : nullptr;
+}
+
+int ensure(Ctx* c, Buf& b, size_t bytes) {
+  if (bytes <= b.cap) return ZDRAW_CUDA_OK;
+  if (b.p) {
+    ZD_CUDA(c, cudaFree(b.p));
+    b.p = nullptr;
+    b.cap = 0;
+  }
+  ZD_CUDA(c, cudaMalloc(&b.p, bytes));
+  b.cap = bytes;
+  return ZDRAW_CUDA_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+size_t dtype_size(uint32_t dt) { return dt == ZDRAW_DTYPE_F32 ? 4 : 2; }
+
+// Resolved, validated view of the params.
+struct Shape {
+  int batch, tokens, heads;
+  long long ld_q, ld_k, ld_v, ld_o;
+  float scale;
+};
+
+int validate(Ctx* c, const zdraw_cuda_attn_params* p, Shape* s) {
+  if (!c) return ZDRAW_CUDA_E_ARG;
+  if (!p) return fail(c, ZDRAW_CUDA_E_ARG, "params is null");
+  if (p->reserved != 0) return fail(c, ZDRAW_CUDA_E_ARG, "params.reserved must be 0");
+  if (p->batch == 0 || p->tokens == 0 || p->heads == 0) return fail(c, ZDRAW_CUDA_E_ARG, "zero batch/tokens/heads");
+  if (p->in_dtype != ZDRAW_DTYPE_F16 && p->in_dtype != ZDRAW_DTYPE_F32)
+    return fail(c, ZDRAW_CUDA_E_ARG, "in_dtype %u is not f16/f32", p->in_dtype);
+  if (p->out_dtype != ZDRAW_DTYPE_F16 && p->out_dtype != ZDRAW_DTYPE_F32)
+    return fail(c, ZDRAW_CUDA_E_ARG, "out_dtype %u is not f16/f32", p->out_dtype);
+  if (p->out_layout > 1 || p->qk_layout > 1 || p->has_key_mask > 1 || p->kernel > 1)
+    return fail(c, ZDRAW_CUDA_E_ARG, "bad layout/flag/kernel code");
+  if (p->txt_tokens > p->tokens) return fail(c, ZDRAW_CUDA_E_ARG, "txt_tokens > tokens");
+  if (!(p->softmax_scale >= 0.0f) || std::isinf(p->softmax_scale))
+    return fail(c, ZDRAW_CUDA_E_ARG, "softmax_scale must be finite and >= 0");
+  if (!(p->norm_eps >= 0.0f)) return fail(c, ZDRAW_CUDA_E_ARG, "norm_eps must be >= 0");
+  // Shapes the kernels do not take: declined, nothing enqueued.
+  if (p->head_dim != kHeadDim) return fail(c, ZDRAW_CUDA_DECLINED, "head_dim %u != 128", p->head_dim);
+  if (p->tokens > kMaxTokens || p->heads > 65535u || p->batch > 65535u)
+    return fail(c, ZDRAW_CUDA_DECLINED, "shape beyond grid limits");
+  const long long dense = static_cast<long long>(p->heads) * kHeadDim;
+  const uint64_t lds[4] = {p->ld_q, p->ld_k, p->ld_v, p->ld_o};
+  long long out[4];
+  for (int i = 0; i < 4; ++i) {
+    out[i] = lds[i] ? static_cast<long long>(lds[i]) : dense;
+    if (out[i] < dense) return fail(c, ZDRAW_CUDA_E_ARG, "token stride %lld < heads*head_dim", out[i]);
+    if (out[i] % 8 != 0 || out[i] > (1ll << 36)) return fail(c, ZDRAW_CUDA_DECLINED, "token stride not a multiple of 8");
+  }
+  if ((p->mask_batch_stride % 4) != 0 || (p->rope_batch_stride % 4) != 0)
+    return fail(c, ZDRAW_CUDA_DECLINED, "mask/rope image stride not a multiple of 4");
+  s->batch = static_cast<int>(p->batch);
+  s->tokens = static_cast<int>(p->tokens);
+  s->heads = static_cast<int>(p->heads);
+  s->ld_q = out[0];
+  s->ld_k = out[1];
+  s->ld_v = out[2];
+  s->ld_o = out[3];
+  s->scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(kHeadDim));
+  ZD_CUDA(c, cudaSetDevice(c->device));  // a context is bound to the device it was created on
+  return ZDRAW_CUDA_OK;
+}
+
+// fp16 tensor [image][token][head][128] (token-major, token stride ld) or
+// [image][head][token][128] (head-major, dense) as a 4-D tiled tensor map with
+// a 64-element x 128-token box and 128-byte swizzle. Dimensions are ordered so
+// that strides grow: (d, head, token, image) token-major, (d, token, head, image)
+// head-major.
+int make_tmap(Ctx* c, CUtensorMap* tm, const void* base, bool head_major, const Shape& s, long long ld) {
+  cuuint64_t dims[4];
+  cuuint64_t strides[3];
+  cuuint32_t box[4];
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (head_major) {
+    dims[0] = kHeadDim; dims[1] = s.tokens; dims[2] = s.heads; dims[3] = s.batch;
+    strides[0] = 2ull * kHeadDim;
+    strides[1] = strides[0] * s.tokens;
+    strides[2] = strides[1] * s.heads;
+    box[0] = 64; box[1] = 128; box[2] = 1; box[3] = 1;
+  } else {
+    dims[0] = kHeadDim; dims[1] = s.heads; dims[2] = s.tokens; dims[3] = s.batch;
+    strides[0] = 2ull * kHeadDim;
+    strides[1] = 2ull * static_cast<cuuint64_t>(ld);
+    strides[2] = strides[1] * s.tokens;
+    box[0] = 64; box[1] = 1; box[2] = 128; box[3] = 1;
+  }
+  const CUresult r = c->encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(c, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return ZDRAW_CUDA_OK;
+}
+
+size_t qk16_bytes(const Shape& s) {
+  return static_cast<size_t>(s.batch) * s.heads * s.tokens * kHeadDim * 2;
+}
+size_t tile_list_ints(const Shape& s) { return static_cast<size_t>((s.tokens + 127) / 128 + 1); }
+
+int reserve_scratch(Ctx* c, const zdraw_cuda_attn_params* p, const Shape& s, bool need_qk) {
+  int rc;
+  if (need_qk) {
+    if ((rc = ensure(c, c->q16, qk16_bytes(s))) != 0) return rc;
+    if ((rc = ensure(c, c->k16, qk16_bytes(s))) != 0) return rc;
+  }
+  if (p->in_dtype == ZDRAW_DTYPE_F32 && (rc = ensure(c, c->v16, qk16_bytes(s))) != 0) return rc;
+  if (p->has_key_mask && (rc = ensure(c, c->tile_list, tile_list_ints(s) * s.batch * sizeof(int))) != 0) return rc;
+  return ZDRAW_CUDA_OK;
+}
+
+int run_prologue(Ctx* c, cudaStream_t stream, const void* q, const void* k, const float* q_w_txt,
+                 const float* q_w_img, const float* k_w_txt, const float* k_w_img, const float* rope_cos,
+                 const float* rope_sin, void* q_out, void* k_out, bool out_head_major,
+                 const zdraw_cuda_attn_params* p, const Shape& s) {
+  const void* ptrs[] = {q, k, q_w_txt, q_w_img, k_w_txt, k_w_img, rope_cos, rope_sin, q_out, k_out};
+  for (const void* x : ptrs) {
+    if (!x) return fail(c, ZDRAW_CUDA_E_ARG, "null pointer given to the prologue");
+    if (!aligned16(x)) return fail(c, ZDRAW_CUDA_E_ARG, "pointer given to the prologue is not 16-byte aligned");
+  }
+  PrologueArgs a;
+  a.batch = s.batch;
+  a.tokens = s.tokens;
+  a.heads = s.heads;
+  a.txt_tokens = static_cast<int>(p->txt_tokens);
+  a.out_head_major = out_head_major ? 1 : 0;
+  a.eps = p->norm_eps;
+  a.q = q;
+  a.k = k;
+  a.ld_q = s.ld_q;
+  a.ld_k = s.ld_k;
+  a.q_w_txt = q_w_txt;
+  a.q_w_img = q_w_img;
+  a.k_w_txt = k_w_txt;
+  a.k_w_img = k_w_img;
+  a.rope_cos = rope_cos;
+  a.rope_sin = rope_sin;
+  a.rope_batch_stride = static_cast<long long>(p->rope_batch_stride);
+  a.q_out = q_out;
+  a.k_out = k_out;
+  ZD_CUDA(c, zdraw::launch_qk_norm_rope(stream, a, p->in_dtype == ZDRAW_DTYPE_F32));
+  return ZDRAW_CUDA_OK;
+}
+
+// q16/k16: fp16 in the given layout (token-major uses ld_q/ld_k). v in in_dtype, token-major.
+int run_attention(Ctx* c, cudaStream_t stream, const void* q16, const void* k16, bool qk_head_major,
+                  long long ld_q16, long long ld_k16, const void* v, const float* key_mask, void* o,
+                  const zdraw_cuda_attn_params* p, const Shape& s) {
+  if (!q16 || !k16 || !v || !o) return fail(c, ZDRAW_CUDA_E_ARG, "null tensor given to attention");
+  if (!aligned16(q16) || !aligned16(k16) || !aligned16(v) || !aligned16(o))
+    return fail(c, ZDRAW_CUDA_E_ARG, "tensor given to attention is not 16-byte aligned");
+  if (p->has_key_mask && (!key_mask || !aligned16(key_mask)))
+    return fail(c, ZDRAW_CUDA_E_ARG, "has_key_mask set but key_mask is null or misaligned");
+  const float* mask = p->has_key_mask ? key_mask : nullptr;
+
+  // f32 v: cast into scratch (dense token-major), as the reference converts v before its
+  // half kernels (metal_api.m:6124-6145, 6790-6815).
+  const void* v16 = v;
+  long long ld_v16 = s.ld_v;
+  if (p->in_dtype == ZDRAW_DTYPE_F32) {
+    int rc = ensure(c, c->v16, qk16_bytes(s));
+    if (rc) return rc;
+    ZD_CUDA(c, zdraw::launch_cast_f32_to_f16(stream, static_cast<const float*>(v), c->v16.p,
+                                             static_cast<long long>(s.batch) * s.tokens, s.heads * kHeadDim,
+                                             s.ld_v));
+    v16 = c->v16.p;
+    ld_v16 = static_cast<long long>(s.heads) * kHeadDim;
+  }
+
+  const bool o_hm = p->out_layout == ZDRAW_LAYOUT_HEAD_MAJOR;
+  const long long o_tok = o_hm ? kHeadDim : s.ld_o;
+  const long long o_head = o_hm ? static_cast<long long>(s.tokens) * kHeadDim : kHeadDim;
+  const long long o_batch = o_hm ? static_cast<long long>(s.heads) * s.tokens * kHeadDim
+                                 : static_cast<long long>(s.tokens) * s.ld_o;
+
+  if (p->kernel == ZDRAW_KERNEL_SCALAR) {
+    ScalarArgs a;
+    a.tokens = s.tokens;
+    a.heads = s.heads;
+    a.batch = s.batch;
+    a.out_f32 = p->out_dtype == ZDRAW_DTYPE_F32;
+    a.scale = s.scale;
+    a.q = static_cast<const __half*>(q16);
+    a.k = static_cast<const __half*>(k16);
+    a.v = static_cast<const __half*>(v16);
+    if (qk_head_major) {
+      a.q_ts = a.k_ts = kHeadDim;
+      a.q_hs = a.k_hs = static_cast<long long>(s.tokens) * kHeadDim;
+      a.q_bs = a.k_bs = static_cast<long long>(s.heads) * s.tokens * kHeadDim;
+    } else {
+      a.q_ts = ld_q16;
+      a.k_ts = ld_k16;
+      a.q_hs = a.k_hs = kHeadDim;
+      a.q_bs = ld_q16 * s.tokens;
+      a.k_bs = ld_k16 * s.tokens;
+    }
+    a.v_ts = ld_v16;
+    a.v_hs = kHeadDim;
+    a.v_bs = ld_v16 * s.tokens;
+    a.key_mask = mask;
+    a.mask_batch_stride = static_cast<long long>(p->mask_batch_stride);
+    a.o = o;
+    a.o_tok_stride = o_tok;
+    a.o_head_stride = o_head;
+    a.o_batch_stride = o_batch;
+    ZD_CUDA(c, zdraw::launch_attn_scalar(stream, a));
+    return ZDRAW_CUDA_OK;
+  }
+
+  CUtensorMap tm_q, tm_k, tm_v;
+  int rc;
+  if ((rc = make_tmap(c, &tm_q, q16, qk_head_major, s, ld_q16)) != 0) return rc;
+  if ((rc = make_tmap(c, &tm_k, k16, qk_head_major, s, ld_k16)) != 0) return rc;
+  if ((rc = make_tmap(c, &tm_v, v16, false, s, ld_v16)) != 0) return rc;
+
+  AttnArgs a;
+  a.tokens = s.tokens;
+  a.heads = s.heads;
+  a.batch = s.batch;
+  a.n_kv_tiles = (s.tokens + 127) / 128;
+  a.q_head_major = a.k_head_major = qk_head_major ? 1 : 0;
+  a.v_head_major = 0;
+  a.out_f32 = p->out_dtype == ZDRAW_DTYPE_F32;
+  a.scale_log2 = s.scale * kLog2e;
+  a.inv_scale = 1.0f / s.scale;
+  a.key_mask = mask;
+  a.mask_batch_stride = static_cast<long long>(p->mask_batch_stride);
+  a.tile_list = nullptr;
+  a.tile_list_stride = 0;
+  if (mask) {
+    const size_t ints = tile_list_ints(s);
+    if ((rc = ensure(c, c->tile_list, ints * s.batch * sizeof(int))) != 0) return rc;
+    ZD_CUDA(c, zdraw::launch_mask_prepare(stream, mask, a.mask_batch_stride, s.tokens, s.batch,
+                                          static_cast<int*>(c->tile_list.p), static_cast<long long>(ints)));
+    a.tile_list = static_cast<const int*>(c->tile_list.p);
+    a.tile_list_stride = static_cast<long long>(ints);
+  }
+  a.o = o;
+  a.o_tok_stride = o_tok;
+  a.o_head_stride = o_head;
+  a.o_batch_stride = o_batch;
+  a.status = c->d_status;
+  ZD_CUDA(c, zdraw::launch_attn_fwd(stream, tm_q, tm_k, tm_v, a));
+  return ZDRAW_CUDA_OK;
+}
+
+int joint(Ctx* c, cudaStream_t stream, const void* q, const void* k, const void* v, const float* q_w_txt,
+          const float* q_w_img, const float* k_w_txt, const float* k_w_img, const float* rope_cos,
+          const float* rope_sin, const float* key_mask, void* o, const zdraw_cuda_attn_params* p,
+          const Shape& s) {
+  int rc = reserve_scratch(c, p, s, true);
+  if (rc) return rc;
+  rc = run_prologue(c, stream, q, k, q_w_txt, q_w_img, k_w_txt, k_w_img, rope_cos, rope_sin, c->q16.p, c->k16.p,
+                    true, p, s);
+  if (rc) return rc;
+  return run_attention(c, stream, c->q16.p, c->k16.p, true, 0, 0, v, key_mask, o, p, s);
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t zdraw_cuda_attn_params_size(void) { return sizeof(zdraw_cuda_attn_params); }
+
+int zdraw_cuda_attn_create(int device, void** ctx_out) {
+  if (!ctx_out) return ZDRAW_CUDA_E_ARG;
+  *ctx_out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return ZDRAW_CUDA_E_CUDA;
+  if (cudaSetDevice(device) != cudaSuccess) return ZDRAW_CUDA_E_CUDA;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return ZDRAW_CUDA_E_CUDA;
+  // The kernels are built for sm_100a only; any other device is declined, not emulated.
+  if (prop.major != 10) return ZDRAW_CUDA_DECLINED;
+  Ctx* c = new (std::nothrow) Ctx();
+  if (!c) return ZDRAW_CUDA_E_CUDA;
+  c->device = device;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
+      qres != cudaDriverEntryPointSuccess) {
+    delete c;
+    return ZDRAW_CUDA_E_CUDA;
+  }
+  c->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  if (cudaMalloc(reinterpret_cast<void**>(&c->d_status), 256) != cudaSuccess ||
+      cudaMemset(c->d_status, 0, 256) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      zdraw::attn_fwd_configure() != cudaSuccess) {
+    if (c->d_status) cudaFree(c->d_status);
+    if (c->host_stream) cudaStreamDestroy(c->host_stream);
+    delete c;
+    return ZDRAW_CUDA_E_CUDA;
+  }
+  *ctx_out = c;
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_attn_destroy(void* ctx) {
+  Ctx* c = as_ctx(ctx);
+  if (!c) return ZDRAW_CUDA_E_ARG;
+  cudaSetDevice(c->device);
+  cudaDeviceSynchronize();
+  Buf* bufs[] = {&c->q16, &c->k16, &c->v16, &c->tile_list, &c->st_q, &c->st_k, &c->st_v,
+                 &c->st_o, &c->st_w, &c->st_cos, &c->st_sin, &c->st_mask};
+  for (Buf* b : bufs)
+    if (b->p) cudaFree(b->p);
+  if (c->d_status) cudaFree(c->d_status);
+  if (c->host_stream) cudaStreamDestroy(c->host_stream);
+  c->magic = 0;
+  delete c;
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_attn_reserve(void* ctx, const zdraw_cuda_attn_params* p) {
+  Ctx* c = as_ctx(ctx);
+  Shape s;
+  int rc = validate(c, p, &s);
+  if (rc) return rc;
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  return reserve_scratch(c, p, s, true);
+}
+
+int zdraw_cuda_qk_norm_rope(void* ctx, void* stream, const void* q, const void* k, const float* q_w_txt,
+                            const float* q_w_img, const float* k_w_txt, const float* k_w_img,
+                            const float* rope_cos, const float* rope_sin, void* q_out_f16, void* k_out_f16,
+                            const zdraw_cuda_attn_params* p) {
+  Ctx* c = as_ctx(ctx);
+  Shape s;
+  int rc = validate(c, p, &s);
+  if (rc) return rc;
+  return run_prologue(c, static_cast<cudaStream_t>(stream), q, k, q_w_txt, q_w_img, k_w_txt, k_w_img, rope_cos,
+                      rope_sin, q_out_f16, k_out_f16, p->qk_layout == ZDRAW_LAYOUT_HEAD_MAJOR, p, s);
+}
+
+int zdraw_cuda_attention(void* ctx, void* stream, const void* q_f16, const void* k_f16, const void* v,
+                         const float* key_mask, void* o, const zdraw_cuda_attn_params* p) {
+  Ctx* c = as_ctx(ctx);
+  Shape s;
+  int rc = validate(c, p, &s);
+  if (rc) return rc;
+  return run_attention(c, static_cast<cudaStream_t>(stream), q_f16, k_f16,
+                       p->qk_layout == ZDRAW_LAYOUT_HEAD_MAJOR, s.ld_q, s.ld_k, v, key_mask, o, p, s);
+}
+
+int zdraw_cuda_joint_attention(void* ctx, void* stream, const void* q, const void* k, const void* v,
+                               const float* q_w_txt, const float* q_w_img, const float* k_w_txt,
+                               const float* k_w_img, const float* rope_cos, const float* rope_sin,
+                               const float* key_mask, void* o, const zdraw_cuda_attn_params* p) {
+  Ctx* c = as_ctx(ctx);
+  Shape s;
+  int rc = validate(c, p, &s);
+  if (rc) return rc;
+  return joint(c, static_cast<cudaStream_t>(stream), q, k, v, q_w_txt, q_w_img, k_w_txt, k_w_img, rope_cos,
+               rope_sin, key_mask, o, p, s);
+}
+
+int zdraw_cuda_joint_attention_host(void* ctx, const void* q, const void* k, const void* v,
+                                    const float* q_w_txt, const float* q_w_img, const float* k_w_txt,
+                                    const float* k_w_img, const float* rope_cos, const float* rope_sin,
+                                    const float* key_mask, void* o, const zdraw_cuda_attn_params* p) {
+  Ctx* c = as_ctx(ctx);
+  Shape s;
+  int rc = validate(c, p, &s);
+  if (rc) return rc;
+  if (!q || !k || !v || !o || !q_w_txt || !q_w_img || !k_w_txt || !k_w_img || !rope_cos || !rope_sin)
+    return fail(c, ZDRAW_CUDA_E_ARG, "null host pointer");
+  if (p->has_key_mask && !key_mask) return fail(c, ZDRAW_CUDA_E_ARG, "has_key_mask set but key_mask is null");
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  const size_t in_sz = dtype_size(p->in_dtype);
+  const size_t out_sz = dtype_size(p->out_dtype);
+  const size_t rows = static_cast<size_t>(s.batch) * s.tokens;
+  const size_t q_bytes = rows * s.ld_q * in_sz, k_bytes = rows * s.ld_k * in_sz, v_bytes = rows * s.ld_v * in_sz;
+  const bool o_hm = p->out_layout == ZDRAW_LAYOUT_HEAD_MAJOR;
+  const size_t o_bytes = (o_hm ? rows * s.heads * kHeadDim : rows * s.ld_o) * out_sz;
+  const size_t rope_elems = p->rope_batch_stride ? static_cast<size_t>(p->rope_batch_stride) * s.batch
+                                                 : static_cast<size_t>(s.tokens) * kHeadDim;
+  const size_t mask_elems = p->mask_batch_stride ? static_cast<size_t>(p->mask_batch_stride) * s.batch
+                                                 : static_cast<size_t>(s.tokens);
+  if ((rc = ensure(c, c->st_q, q_bytes)) || (rc = ensure(c, c->st_k, k_bytes)) || (rc = ensure(c, c->st_v, v_bytes)) ||
+      (rc = ensure(c, c->st_o, o_bytes)) || (rc = ensure(c, c->st_w, 4 * kHeadDim * sizeof(float))) ||
+      (rc = ensure(c, c->st_cos, rope_elems * sizeof(float))) ||
+      (rc = ensure(c, c->st_sin, rope_elems * sizeof(float))))
+    return rc;
+  if (p->has_key_mask && (rc = ensure(c, c->st_mask, mask_elems * sizeof(float)))) return rc;
+  cudaStream_t st = c->host_stream;
+  float* w = static_cast<float*>(c->st_w.p);
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_q.p, q, q_bytes, cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_k.p, k, k_bytes, cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_v.p, v, v_bytes, cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(w, q_w_txt, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(w + kHeadDim, q_w_img, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(w + 2 * kHeadDim, k_w_txt, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(w + 3 * kHeadDim, k_w_img, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_cos.p, rope_cos, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_sin.p, rope_sin, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st));
+  if (p->has_key_mask)
+    ZD_CUDA(c, cudaMemcpyAsync(c->st_mask.p, key_mask, mask_elems * sizeof(float), cudaMemcpyHostToDevice, st));
+  rc = joint(c, st, c->st_q.p, c->st_k.p, c->st_v.p, w, w + kHeadDim, w + 2 * kHeadDim, w + 3 * kHeadDim,
+             static_cast<const float*>(c->st_cos.p), static_cast<const float*>(c->st_sin.p),
+             static_cast<const float*>(c->st_mask.p), c->st_o.p, p, s);
+  if (rc) return rc;
+  ZD_CUDA(c, cudaMemcpyAsync(o, c->st_o.p, o_bytes, cudaMemcpyDeviceToHost, st));
+  ZD_CUDA(c, cudaStreamSynchronize(st));
+  uint32_t status = 0;
+  ZD_CUDA(c, cudaMemcpy(&status, c->d_status, sizeof(status), cudaMemcpyDeviceToHost));
+  if (status != 0) return fail(c, ZDRAW_CUDA_E_DEVICE, "kernel gave up a bounded wait (status 0x%x)", status);
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_attention_host(void* ctx, const void* q, const void* k, const void* v, const float* key_mask,
+                              void* o, const zdraw_cuda_attn_params* p) {
+  Ctx* c = as_ctx(ctx);
+  Shape s;
+  int rc = validate(c, p, &s);
+  if (rc) return rc;
+  if (!q || !k || !v || !o) return fail(c, ZDRAW_CUDA_E_ARG, "null host pointer");
+  if (p->has_key_mask && !key_mask) return fail(c, ZDRAW_CUDA_E_ARG, "has_key_mask set but key_mask is null");
+  const bool f32 = p->in_dtype == ZDRAW_DTYPE_F32;
+  const size_t in_sz = dtype_size(p->in_dtype);
+  const size_t out_sz = dtype_size(p->out_dtype);
+  const size_t rows = static_cast<size_t>(s.batch) * s.tokens;
+  const size_t q_bytes = rows * s.ld_q * in_sz, k_bytes = rows * s.ld_k * in_sz, v_bytes = rows * s.ld_v * in_sz;
+  const bool o_hm = p->out_layout == ZDRAW_LAYOUT_HEAD_MAJOR;
+  const size_t o_bytes = (o_hm ? rows * s.heads * kHeadDim : rows * s.ld_o) * out_sz;
+  const size_t mask_elems = p->mask_batch_stride ? static_cast<size_t>(p->mask_batch_stride) * s.batch
+                                                 : static_cast<size_t>(s.tokens);
+  if ((rc = ensure(c, c->st_q, q_bytes)) || (rc = ensure(c, c->st_k, k_bytes)) || (rc = ensure(c, c->st_v, v_bytes)) ||
+      (rc = ensure(c, c->st_o, o_bytes)))
+    return rc;
+  if (p->has_key_mask && (rc = ensure(c, c->st_mask, mask_elems * sizeof(float)))) return rc;
+  if (f32 && ((rc = ensure(c, c->q16, qk16_bytes(s))) || (rc = ensure(c, c->k16, qk16_bytes(s))))) return rc;
+  cudaStream_t st = c->host_stream;
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_q.p, q, q_bytes, cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_k.p, k, k_bytes, cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_v.p, v, v_bytes, cudaMemcpyHostToDevice, st));
+  if (p->has_key_mask)
+    ZD_CUDA(c, cudaMemcpyAsync(c->st_mask.p, key_mask, mask_elems * sizeof(float), cudaMemcpyHostToDevice, st));
+  const void* q16 = c->st_q.p;
+  const void* k16 = c->st_k.p;
+  long long ld_q16 = s.ld_q, ld_k16 = s.ld_k;
+  if (f32) {
+    // f32 q/k are cast to fp16 (dense token-major) before the kernel, as the reference's
+    // half kernels require (to_headmajor_f16, metal_api.m:6124-6145).
+    const int row_elems = s.heads * kHeadDim;
+    ZD_CUDA(c, zdraw::launch_cast_f32_to_f16(st, static_cast<const float*>(c->st_q.p), c->q16.p,
+                                             static_cast<long long>(rows), row_elems, s.ld_q));
+    ZD_CUDA(c, zdraw::launch_cast_f32_to_f16(st, static_cast<const float*>(c->st_k.p), c->k16.p,
+                                             static_cast<long long>(rows), row_elems, s.ld_k));
+    q16 = c->q16.p;
+    k16 = c->k16.p;
+    ld_q16 = ld_k16 = row_elems;
+  }
+  rc = run_attention(c, st, q16, k16, false, ld_q16, ld_k16, c->st_v.p, static_cast<const float*>(c->st_mask.p),
+                     c->st_o.p, p, s);
+  if (rc) return rc;
+  ZD_CUDA(c, cudaMemcpyAsync(o, c->st_o.p, o_bytes, cudaMemcpyDeviceToHost, st));
+  ZD_CUDA(c, cudaStreamSynchronize(st));
+  uint32_t status = 0;
+  ZD_CUDA(c, cudaMemcpy(&status, c->d_status, sizeof(status), cudaMemcpyDeviceToHost));
+  if (status != 0) return fail(c, ZDRAW_CUDA_E_DEVICE, "kernel gave up a bounded wait (status 0x%x)", status);
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_last_status(void* ctx, void* stream, uint32_t* device_status) {
+  Ctx* c = as_ctx(ctx);
+  if (!c || !device_status) return ZDRAW_CUDA_E_ARG;
+  ZD_CUDA(c, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  ZD_CUDA(c, cudaMemcpy(device_status, c->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+  if (*device_status != 0) ZD_CUDA(c, cudaMemset(c->d_status, 0, sizeof(uint32_t)));
+  return ZDRAW_CUDA_OK;
+}
+
+const char* zdraw_cuda_last_error(void* ctx) {
+  Ctx* c = as_ctx(ctx);
+  return c ? c->err : "invalid context";
+}
+
+// --------------------------------------------------------------------------- host-side RoPE tables
+
+int zdraw_cuda_klein_rope_table(float* cos_out, float* sin_out, size_t txt_len, size_t grid_h, size_t grid_w,
+                                size_t ref_h, size_t ref_w, double theta) {
+  if (!cos_out || !sin_out || !(theta > 0.0)) return ZDRAW_CUDA_E_ARG;
+  if ((grid_h == 0) != (grid_w == 0) || (ref_h == 0) != (ref_w == 0)) return ZDRAW_CUDA_E_ARG;
+  // 16 frequencies per 32-wide axis, shared by the four axes.
+  double freq[16];
+  for (int i = 0; i < 16; ++i) freq[i] = 1.0 / std::pow(theta, static_cast<double>(2 * i) / 32.0);
+  const size_t img = grid_h * grid_w;
+  const size_t total = txt_len + img + ref_h * ref_w;
+  for (size_t t = 0; t < total; ++t) {
+    double id[4] = {0.0, 0.0, 0.0, 0.0};  // (T, H, W, L)
+    if (t < txt_len) {
+      id[3] = static_cast<double>(t);
+    } else if (t < txt_len + img) {
+      id[1] = static_cast<double>((t - txt_len) / grid_w);
+      id[2] = static_cast<double>((t - txt_len) % grid_w);
+    } else {
+      id[0] = 10.0;
+      id[1] = static_cast<double>((t - txt_len - img) / ref_w);
+      id[2] = static_cast<double>((t - txt_len - img) % ref_w);
+    }
+    float* c = cos_out + t * kHeadDim;
+    float* s = sin_out + t * kHeadDim;
+    for (int ax = 0; ax < 4; ++ax)
+      for (int i = 0; i < 16; ++i) {
+        const double ang = id[ax] * freq[i];
+        c[ax * 32 + 2 * i] = c[ax * 32 + 2 * i + 1] = static_cast<float>(std::cos(ang));
+        s[ax * 32 + 2 * i] = s[ax * 32 + 2 * i + 1] = static_cast<float>(std::sin(ang));
+      }
+  }
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_zimage_rope_table(float* cos_out, float* sin_out, size_t img_h, size_t img_w, size_t cap_total,
+                                 const size_t dims[3], const size_t lens[3], float theta) {
+  if (!cos_out || !sin_out || !dims || !lens) return ZDRAW_CUDA_E_ARG;
+  if (!(theta > 0.0f)) return ZDRAW_CUDA_E_ARG;
+  size_t width = 0;
+  for (int a = 0; a < 3; ++a) {
+    if (dims[a] == 0 || lens[a] == 0 || dims[a] % 2 != 0) return ZDRAW_CUDA_E_ARG;
+    width += dims[a];
+  }
+  if (width != kHeadDim) return ZDRAW_CUDA_E_ARG;
+  const size_t n_img = img_h * img_w;
+  const float neg_log_theta = -std::log(theta);
+  for (size_t t = 0; t < n_img + cap_total; ++t) {
+    size_t pos[3];
+    if (t < n_img) {  // image tokens come first
+      pos[0] = cap_total + 1;
+      pos[1] = t / img_w;
+      pos[2] = t % img_w;
+    } else {
+      pos[0] = 1 + (t - n_img);
+      pos[1] = 0;
+      pos[2] = 0;
+    }
+    size_t col = 0;
+    for (int a = 0; a < 3; ++a) {
+      if (pos[a] >= lens[a]) return ZDRAW_CUDA_E_ARG;  // BadPosition
+      const float fpos = static_cast<float>(pos[a]);
+      for (size_t pr = 0; pr < dims[a] / 2; ++pr) {
+        const float power = 2.0f * static_cast<float>(pr) / static_cast<float>(dims[a]);
+        const float ang = fpos * std::exp(neg_log_theta * power);
+        const size_t o = t * kHeadDim + col + 2 * pr;
+        cos_out[o] = cos_out[o + 1] = std::cos(ang);
+        sin_out[o] = sin_out[o + 1] = std::sin(ang);
+      }
+      col += dims[a];
+    }
+  }
+  return ZDRAW_CUDA_OK;
+}
+
+}  // extern "C"

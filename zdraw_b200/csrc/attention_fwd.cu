@@ -1,0 +1,566 @@
+// Non-causal flash attention forward for head_dim 128 on sm_100a.
+//
+// Replaces the reference's fast attention kernels for the DiT path
+// (vendor/steel attn_entry.metal:39-46 `steel_attn_h128`, the MFA kernel
+// vendor/mfa/mfa-fwd-d128.metal:408-1541 and src/metal/mattn_block_shader.zig:24-187)
+// with one warp-specialised kernel:
+//
+//   warp 0      TMA producer: Q tiles once, then K_j / V_j tiles through a ring of
+//               128B-swizzled shared-memory stages (cp.async.bulk.tensor, no multicast)
+//   warp 1      MMA issuer: tcgen05.mma, S = Q K^T (both operands in shared memory)
+//               and O += P V (P read from tensor memory), accumulators in TMEM
+//   warps 4-7   softmax for query tile 0, one thread per query row
+//   warps 8-11  softmax for query tile 1
+// (warps 2-3 idle; the first warpgroup gives most of its registers to the softmax
+// warpgroups with setmaxnreg, so a softmax thread can hold a whole 128-score row)
+//
+// A CTA owns two 128-row query tiles of one (image, head) and walks all keys, so a
+// row's reduction order is fixed: no split-KV, no atomics, repeated runs are
+// bit-identical. The two tiles ping-pong: while the softmax warps work on one
+// tile's scores the tensor core runs the other tile's MMAs.
+//
+// Softmax is the exp2 form all three reference kernels use
+// (steel_attention.h:166, mfa-fwd-d128.metal:999, mattn_block_shader.zig:39):
+// p = exp2(s*scale*log2e - m*scale*log2e), fp32 running max m and sum l.
+// The accumulator rescale is lazy: O and l are rescaled only when a row's max grew
+// by more than 2^8, a decision that depends on the data alone.
+//
+// TMEM columns: [0,128) S/P tile 0, [128,256) S/P tile 1, [256,384) O tile 0,
+// [384,512) O tile 1. P (fp16) overwrites the first 64 columns of its S.
+#include "attention_fwd.cuh"
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "ptx.cuh"
+
+namespace zdraw {
+
+namespace {
+
+constexpr int kBM = 128;           // query rows per tile
+constexpr int kBN = 128;           // keys per K/V tile
+constexpr int kStages = 4;         // K/V ring depth (one tile per stage)
+constexpr int kTileBytes = 32768;  // 128 rows x 128 f16
+constexpr int kHalfBytes = 16384;  // 128 rows x 64 f16: one 128B-swizzled block
+constexpr int kThreads = 384;
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
+constexpr float kRescaleThreshold = 8.0f;                       // log2 units
+// Register budgets after setmaxnreg: per SM sub-partition one warp of each warpgroup is
+// resident, and 80 + 216 + 216 = 512 (= 16384 registers / 32 lanes).
+constexpr int kRegsControl = 80;
+constexpr int kRegsSoftmax = 216;
+
+// Shared-memory carve-up (offsets from a 1024-byte aligned base).
+constexpr int kOffQ = 0;
+constexpr int kOffKV = 2 * kTileBytes;
+constexpr int kOffBar = kOffKV + kStages * kTileBytes;
+// barrier slots (8 bytes each)
+constexpr int kBarQFull = 0;                      // [2]
+constexpr int kBarKVFull = 2;                     // [kStages]
+constexpr int kBarKVEmpty = 2 + kStages;          // [kStages]
+constexpr int kBarSFull = 2 + 2 * kStages;        // [2]
+constexpr int kBarPFull = 4 + 2 * kStages;        // [2]
+constexpr int kBarOFull = 6 + 2 * kStages;        // [2]
+constexpr int kBarDrain = 8 + 2 * kStages;        // [1]
+constexpr int kNumBars = 9 + 2 * kStages;
+constexpr int kOffFlags = kOffBar + kNumBars * 8;  // u32 abort, u32 tmem base
+constexpr int kSmemBytes = kOffFlags + 16 + 1024;  // + alignment slack
+
+// Status codes OR-ed into the device status word when a bounded wait gives up.
+constexpr uint32_t kStProducer = 1u << 0;
+constexpr uint32_t kStMma = 1u << 1;
+constexpr uint32_t kStSoftmax = 1u << 2;
+
+// Tile-list entries: K/V tile index, plus a flag for tiles the key mask covers partly.
+constexpr int kTileMixedFlag = 0x40000000;
+constexpr int kTileIndexMask = 0x3FFFFFFF;
+
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                         uint32_t* status, uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void store_row_chunk(const AttnArgs& a, size_t row_off, int col,
+                                                const float* v) {
+  // 32 consecutive output columns of one row, starting at `col`.
+  if (a.out_f32) {
+    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(a.o) + row_off + col);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(a.o) + row_off + col);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 w;
+      w.x = pack_f16x2(v[8 * i + 0], v[8 * i + 1]);
+      w.y = pack_f16x2(v[8 * i + 2], v[8 * i + 3]);
+      w.z = pack_f16x2(v[8 * i + 4], v[8 * i + 5]);
+      w.w = pack_f16x2(v[8 * i + 6], v[8 * i + 7]);
+      dst[i] = w;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* sbase = smem_raw + (base - raw_addr);
+  volatile uint32_t* flags = reinterpret_cast<volatile uint32_t*>(sbase + kOffFlags);
+  volatile uint32_t* abort_flag = flags;
+  auto bar = [&](int i) -> uint32_t { return base + kOffBar + 8u * static_cast<uint32_t>(i); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q_tile0 = blockIdx.x * 2;
+  const int head = blockIdx.y;
+  const int img = blockIdx.z;
+
+  if (threadIdx.x == 0) {
+    // A kernel that already gave up on this context makes later CTAs return at once.
+    flags[0] = (*reinterpret_cast<volatile uint32_t*>(a.status) != 0u) ? 1u : 0u;
+    flags[1] = 0u;
+    mbar_init(bar(kBarQFull + 0), 1);
+    mbar_init(bar(kBarQFull + 1), 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar(kBarKVFull + s), 1);
+      mbar_init(bar(kBarKVEmpty + s), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar(kBarSFull + t), 1);
+      mbar_init(bar(kBarPFull + t), kBM);
+      mbar_init(bar(kBarOFull + t), 1);
+    }
+    mbar_init(bar(kBarDrain), 1);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+
+  if (warp == 1) {
+    tmem_alloc(base + kOffFlags + 4, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = flags[1];
+
+  // Coordinates of (token row, head) in the two tensor-map dimension orders.
+  auto c1 = [&](int hm, int tok) { return hm ? tok : head; };
+  auto c2 = [&](int hm, int tok) { return hm ? head : tok; };
+
+  // Active K/V tiles of this image: all of them, or the list a key mask left.
+  const int* tile_list = a.tile_list ? a.tile_list + static_cast<size_t>(img) * a.tile_list_stride : nullptr;
+  const int n_act = tile_list ? tile_list[0] : a.n_kv_tiles;
+  auto tile_entry = [&](int jj) -> int { return tile_list ? tile_list[1 + jj] : jj; };
+
+  if (warp < 4) {
+    reg_dealloc<kRegsControl>();
+    if (warp == 0) {
+      // ---------------------------------------------------------- TMA producer
+      if (lane == 0 && n_act > 0) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        for (int t = 0; t < 2; ++t) {
+          const int row = (q_tile0 + t) * kBM;
+          const uint32_t dst = base + kOffQ + t * kTileBytes;
+          mbar_arrive_expect_tx(bar(kBarQFull + t), kTileBytes);
+          tma_load_4d(dst, &tm_q, bar(kBarQFull + t), 0, c1(a.q_head_major, row), c2(a.q_head_major, row), img);
+          tma_load_4d(dst + kHalfBytes, &tm_q, bar(kBarQFull + t), 64, c1(a.q_head_major, row),
+                      c2(a.q_head_major, row), img);
+        }
+        uint32_t it = 0;
+        bool ok = true;
+        for (int jj = 0; jj < n_act && ok; ++jj) {
+          const int row = (tile_entry(jj) & kTileIndexMask) * kBN;
+          for (int which = 0; which < 2; ++which, ++it) {
+            const uint32_t stage = it % kStages;
+            const uint32_t phase = (it / kStages) & 1u;
+            ok = wait_bar(bar(kBarKVEmpty + stage), phase ^ 1u, abort_flag, a.status, kStProducer);
+            if (!ok) break;
+            const uint32_t dst = base + kOffKV + stage * kTileBytes;
+            const CUtensorMap* tm = which ? &tm_v : &tm_k;
+            const int hm = which ? a.v_head_major : a.k_head_major;
+            mbar_arrive_expect_tx(bar(kBarKVFull + stage), kTileBytes);
+            tma_load_4d(dst, tm, bar(kBarKVFull + stage), 0, c1(hm, row), c2(hm, row), img);
+            tma_load_4d(dst + kHalfBytes, tm, bar(kBarKVFull + stage), 64, c1(hm, row), c2(hm, row), img);
+          }
+        }
+        if (!ok) {
+          // Let copies that are still in flight land before the CTA's shared memory goes away.
+          for (int i = 0; i < 100; ++i) __nanosleep(1000);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ---------------------------------------------------------- MMA issuer
+      if (lane == 0 && n_act > 0) {
+        constexpr uint32_t idesc_qk = umma_idesc_f16(kBM, kBN, 0, 0);
+        constexpr uint32_t idesc_pv = umma_idesc_f16(kBM, 128, 0, 1);
+
+        // S_t = Q_t K^T: the K dimension is head_dim 128 = 8 steps of 16; a step moves 32
+        // bytes inside a 128-byte swizzled row, the second 64 columns live in the next block.
+        auto issue_qk = [&](int t, uint32_t k_addr) {
+          const uint64_t desc_q = smem_desc_sw128(base + kOffQ + t * kTileBytes, 16, 1024);
+          const uint64_t desc_k = smem_desc_sw128(k_addr, 16, 1024);
+          const uint32_t d_tmem = tmem_base + 128u * t;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = static_cast<uint32_t>((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+            umma_ss(d_tmem, desc_q + off, desc_k + off, idesc_qk, k > 0 ? 1u : 0u);
+          }
+        };
+        // O_t (+)= P_t V: the K dimension is 128 keys = 8 steps of 16 keys (2048 bytes of V
+        // rows, 8 TMEM columns of packed f16 P); N = head_dim spans two 64-column blocks (LBO).
+        auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate) {
+          const uint64_t desc_v = smem_desc_sw128(v_addr, kHalfBytes, 1024);
+          const uint32_t p_tmem = tmem_base + 128u * t;
+          const uint32_t d_tmem = tmem_base + 256u + 128u * t;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            umma_ts(d_tmem, p_tmem + 8u * k, desc_v + ((2048u * k) >> 4), idesc_pv,
+                    (accumulate || k > 0) ? 1u : 0u);
+          }
+        };
+
+        bool ok = wait_bar(bar(kBarQFull + 0), 0, abort_flag, a.status, kStMma) &&
+                  wait_bar(bar(kBarQFull + 1), 0, abort_flag, a.status, kStMma);
+        uint32_t it = 0;
+        if (ok) ok = wait_bar(bar(kBarKVFull + 0), 0, abort_flag, a.status, kStMma);
+        if (ok) {
+          tc_fence_after();
+          const uint32_t k_addr = base + kOffKV;
+          issue_qk(0, k_addr);
+          umma_commit(bar(kBarSFull + 0));
+          issue_qk(1, k_addr);
+          umma_commit(bar(kBarSFull + 1));
+          umma_commit(bar(kBarKVEmpty + 0));
+          it = 1;
+        }
+        for (int jj = 0; jj < n_act && ok; ++jj) {
+          const uint32_t sv = it % kStages;
+          const uint32_t phv = (it / kStages) & 1u;
+          ++it;
+          ok = wait_bar(bar(kBarKVFull + sv), phv, abort_flag, a.status, kStMma);
+          if (!ok) break;
+          const bool has_next = (jj + 1 < n_act);
+          uint32_t sk = 0;
+          if (has_next) {
+            sk = it % kStages;
+            const uint32_t phk = (it / kStages) & 1u;
+            ++it;
+            ok = wait_bar(bar(kBarKVFull + sk), phk, abort_flag, a.status, kStMma);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          const uint32_t v_addr = base + kOffKV + sv * kTileBytes;
+          const uint32_t k_addr = base + kOffKV + sk * kTileBytes;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            ok = wait_bar(bar(kBarPFull + t), static_cast<uint32_t>(jj) & 1u, abort_flag, a.status, kStMma);
+            if (!ok) break;
+            tc_fence_after();
+            issue_pv(t, v_addr, jj > 0);
+            if (has_next) {
+              issue_qk(t, k_addr);
+              umma_commit(bar(kBarSFull + t));
+            } else {
+              umma_commit(bar(kBarOFull + t));
+            }
+          }
+          if (!ok) break;
+          umma_commit(bar(kBarKVEmpty + sv));
+          if (has_next) umma_commit(bar(kBarKVEmpty + sk));
+        }
+        if (!ok) {
+          // Wait (bounded) for MMAs already issued before TMEM is released.
+          umma_commit(bar(kBarDrain));
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(bar(kBarDrain), 0) && globaltimer_ns() - t0 < kWaitLimitNs) {
+          }
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    reg_alloc<kRegsSoftmax>();
+    // ------------------------------------------------------------ softmax + epilogue
+    const int t = (warp - 4) >> 2;          // query tile of this warp group
+    const int quarter = warp & 3;           // TMEM lanes this warp may touch
+    const int row = quarter * 32 + lane;    // row inside the tile
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t t_s = tmem_base + 128u * t + lane_off;
+    const uint32_t t_o = tmem_base + 256u + 128u * t + lane_off;
+    const float c = a.scale_log2;
+    const int last_tile = a.n_kv_tiles - 1;
+    const int tail = a.tokens - last_tile * kBN;  // valid keys in the last tile (1..128)
+    const float* mask = a.key_mask ? a.key_mask + static_cast<size_t>(img) * a.mask_batch_stride : nullptr;
+
+    float m = -INFINITY;  // running row max of raw scores
+    float l = 0.0f;       // running row sum of p
+    bool ok = true;
+
+    for (int jj = 0; jj < n_act; ++jj) {
+      const int entry = tile_entry(jj);
+      const int tile = entry & kTileIndexMask;
+      ok = __all_sync(0xffffffffu,
+                      wait_bar(bar(kBarSFull + t), static_cast<uint32_t>(jj) & 1u, abort_flag, a.status, kStSoftmax));
+      if (!ok) break;
+      tc_fence_after();
+
+      if (entry & kTileMixedFlag) {
+        // A tile the key mask covers partly (rare): add the mask, and -inf beyond the last
+        // key, to the scores in place in TMEM, 32 columns at a time.
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t x[32];
+          tmem_ld_x32(t_s + 32u * ch, x);
+          tmem_wait_ld();
+          const int key0 = tile * kBN + 32 * ch;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + i;
+            const float mv = (key < a.tokens) ? __ldg(mask + key) : -INFINITY;
+            x[i] = __float_as_uint((mv == -INFINITY) ? -INFINITY : fmaf(mv, a.inv_scale, __uint_as_float(x[i])));
+          }
+          tmem_st_x32(t_s + 32u * ch, x);
+          tmem_wait_st();
+        }
+      }
+
+      uint32_t sr[128];
+      tmem_ld_x32(t_s + 0, sr + 0);
+      tmem_ld_x32(t_s + 32, sr + 32);
+      tmem_ld_x32(t_s + 64, sr + 64);
+      tmem_ld_x32(t_s + 96, sr + 96);
+      tmem_wait_ld();
+      float* s = reinterpret_cast<float*>(sr);
+
+      if (tile_list == nullptr && tile == last_tile && tail < kBN) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) s[i] = (i < tail) ? s[i] : -INFINITY;
+      }
+
+      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+#pragma unroll
+      for (int i = 4; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, s[i]);
+        mx1 = fmaxf(mx1, s[i + 1]);
+        mx2 = fmaxf(mx2, s[i + 2]);
+        mx3 = fmaxf(mx3, s[i + 3]);
+      }
+      const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+
+      if (jj == 0) {
+        m = m_new;
+      } else {
+        // PV of the previous step has completed: the commit that released S covers it.
+        const bool need = (m_new - m) * c > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          float alpha = 1.0f;
+          if (need) {
+            alpha = ex2_approx((m - m_new) * c);
+            m = m_new;
+          }
+          l *= alpha;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t o[32];
+            tmem_ld_x32(t_o + 32u * ch, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_x32(t_o + 32u * ch, o);
+          }
+          tmem_wait_st();
+        }
+      }
+
+      const float mc = (m == -INFINITY) ? 0.0f : m * c;
+      float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = ex2_approx(fmaf(s[32 * ch + 2 * i], c, -mc));
+          const float p1 = ex2_approx(fmaf(s[32 * ch + 2 * i + 1], c, -mc));
+          sum0 += p0;
+          sum1 += p1;
+          pk[i] = pack_f16x2(p0, p1);
+        }
+        tmem_st_x16(t_s + 16u * ch, pk);
+      }
+      l += sum0 + sum1;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(kBarPFull + t));
+    }
+
+    if (ok && n_act > 0)
+      ok = __all_sync(0xffffffffu, wait_bar(bar(kBarOFull + t), 0, abort_flag, a.status, kStSoftmax));
+    if (ok) {
+      tc_fence_after();
+      // A row whose every key is masked has l == 0 and is written as zeros.
+      const float inv_l = (l > 0.0f) ? 1.0f / l : 0.0f;
+      const int tok = (q_tile0 + t) * kBM + row;
+      const size_t row_off = static_cast<size_t>(img) * a.o_batch_stride +
+                             static_cast<size_t>(tok) * a.o_tok_stride +
+                             static_cast<size_t>(head) * a.o_head_stride;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t o[32];
+        if (n_act > 0) {
+          tmem_ld_x32(t_o + 32u * ch, o);
+          tmem_wait_ld();
+        }
+        if (tok < a.tokens) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = (n_act > 0) ? __uint_as_float(o[i]) * inv_l : 0.0f;
+          store_row_chunk(a, row_off, 32 * ch, v);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------
+// Scalar cross-check kernel: one warp per (image, head, query row), lanes split
+// head_dim, online softmax over keys in order, natural exp. Slow; tests only.
+// It reads the same fp16 q/k/v through the same strides as the tcgen05 kernel.
+// ---------------------------------------------------------------------------
+__global__ void attn_scalar_kernel(const ScalarArgs a) {
+  const int warp_in_block = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long gw = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp_in_block;
+  const long long rows = static_cast<long long>(a.batch) * a.heads * a.tokens;
+  if (gw >= rows) return;
+  const int tok = static_cast<int>(gw % a.tokens);
+  const int head = static_cast<int>((gw / a.tokens) % a.heads);
+  const int img = static_cast<int>(gw / (static_cast<long long>(a.tokens) * a.heads));
+
+  const __half* q = a.q + img * a.q_bs + tok * a.q_ts + head * a.q_hs + lane * 4;
+  const __half* kb = a.k + img * a.k_bs + head * a.k_hs + lane * 4;
+  const __half* vb = a.v + img * a.v_bs + head * a.v_hs + lane * 4;
+  const float* mask = a.key_mask ? a.key_mask + static_cast<size_t>(img) * a.mask_batch_stride : nullptr;
+
+  float qf[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int i = 0; i < 4; ++i) qf[i] = __half2float(q[i]);
+  float m = -INFINITY, l = 0.0f;
+  for (int j = 0; j < a.tokens; ++j) {
+    const __half* k = kb + static_cast<size_t>(j) * a.k_ts;
+    float d = 0.0f;
+    for (int i = 0; i < 4; ++i) d += qf[i] * __half2float(k[i]);
+    for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+    float s = d * a.scale;
+    if (mask) s += mask[j];
+    if (s == -INFINITY) continue;
+    const float m_new = fmaxf(m, s);
+    const float alpha = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+    const float p = expf(s - m_new);
+    const __half* v = vb + static_cast<size_t>(j) * a.v_ts;
+    for (int i = 0; i < 4; ++i) acc[i] = acc[i] * alpha + p * __half2float(v[i]);
+    l = l * alpha + p;
+    m = m_new;
+  }
+  const float inv_l = l > 0.0f ? 1.0f / l : 0.0f;
+  const size_t off = static_cast<size_t>(img) * a.o_batch_stride + static_cast<size_t>(tok) * a.o_tok_stride +
+                     static_cast<size_t>(head) * a.o_head_stride + lane * 4;
+  if (a.out_f32) {
+    float* o = static_cast<float*>(a.o) + off;
+    for (int i = 0; i < 4; ++i) o[i] = acc[i] * inv_l;
+  } else {
+    __half* o = static_cast<__half*>(a.o) + off;
+    for (int i = 0; i < 4; ++i) o[i] = __float2half_rn(acc[i] * inv_l);
+  }
+}
+
+
+// ---------------------------------------------------------------------------
+// Key-mask tile classification. One block per image, 128 threads = one tile's keys.
+// A tile is left out when every one of its keys is masked (-inf or beyond the
+// sequence), listed plain when all 128 keys exist and carry mask 0, else listed
+// with the mixed flag. Tiles stay in ascending order, so the reduction order over
+// keys does not depend on the mask.
+// ---------------------------------------------------------------------------
+__global__ void mask_prepare_kernel(const float* key_mask, long long mask_batch_stride, int tokens,
+                                    int n_kv_tiles, int* tile_list, long long list_stride) {
+  const float* mask = key_mask + static_cast<size_t>(blockIdx.x) * mask_batch_stride;
+  int* list = tile_list + static_cast<size_t>(blockIdx.x) * list_stride;
+  for (int j = 0; j < n_kv_tiles; ++j) {
+    const int key = j * kBN + static_cast<int>(threadIdx.x);
+    const bool exists = key < tokens;
+    const float mv = exists ? mask[key] : -INFINITY;
+    const int all_masked = __syncthreads_and(mv == -INFINITY);
+    const int all_zero = __syncthreads_and(exists && mv == 0.0f);
+    if (threadIdx.x == 0) list[1 + j] = all_masked ? -1 : (all_zero ? j : (j | kTileMixedFlag));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int j = 0; j < n_kv_tiles; ++j) {
+      const int e = list[1 + j];
+      if (e >= 0) list[1 + n++] = e;
+    }
+    list[0] = n;
+  }
+}
+
+}  // namespace
+
+int attn_fwd_smem_bytes() { return kSmemBytes; }
+
+cudaError_t attn_fwd_configure() {
+  return cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+}
+
+cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
+                            const CUtensorMap& tm_v, const AttnArgs& args) {
+  const int n_q_tiles = (args.tokens + kBM - 1) / kBM;
+  dim3 grid((n_q_tiles + 1) / 2, args.heads, args.batch);
+  attn_fwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, args);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args) {
+  const long long rows = static_cast<long long>(args.batch) * args.heads * args.tokens;
+  const int warps_per_block = 8;
+  const long long blocks = (rows + warps_per_block - 1) / warps_per_block;
+  attn_scalar_kernel<<<static_cast<unsigned>(blocks), warps_per_block * 32, 0, stream>>>(args);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_mask_prepare(cudaStream_t stream, const float* key_mask, long long mask_batch_stride,
+                                int tokens, int batch, int* tile_list, long long list_stride) {
+  const int n_kv_tiles = (tokens + kBN - 1) / kBN;
+  mask_prepare_kernel<<<batch, kBN, 0, stream>>>(key_mask, mask_batch_stride, tokens, n_kv_tiles, tile_list,
+                                                 list_stride);
+  return cudaGetLastError();
+}
+
+}  // namespace zdraw

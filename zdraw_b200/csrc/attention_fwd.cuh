@@ -1,0 +1,61 @@
+// Launch interface of the attention kernels (internal to the library).
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace zdraw {
+
+// Arguments of the tcgen05 kernel besides its three tensor maps. q, k and v are
+// reached only through the tensor maps: 4-D, fp16, 128-byte swizzle, box 64 x 128 rows.
+// Dimension order is (d, token, head, image) for a head-major tensor and
+// (d, head, token, image) for a token-major one, so that strides grow with the
+// dimension; *_head_major tells the kernel which order a map uses.
+struct AttnArgs {
+  int tokens;      // S
+  int heads;       // H
+  int batch;       // images
+  int n_kv_tiles;  // ceil(S / 128)
+  int q_head_major, k_head_major, v_head_major;
+  int out_f32;         // 1: o is f32, 0: o is f16
+  float scale_log2;    // softmax_scale * log2(e)
+  float inv_scale;     // 1 / softmax_scale (turns the additive mask into raw-score units)
+  const float* key_mask;       // [S] additive, or nullptr
+  long long mask_batch_stride;  // elements between images (0 = shared)
+  // With a key mask: per image [count, entry...] written by launch_mask_prepare. An entry is
+  // a K/V tile index, | 0x40000000 when the mask (or the end of the sequence) covers the
+  // tile partly. Tiles whose every key is masked are left out. nullptr without a mask.
+  const int* tile_list;
+  long long tile_list_stride;  // ints between images
+  void* o;
+  long long o_tok_stride, o_head_stride, o_batch_stride;  // elements
+  uint32_t* status;  // device status word
+};
+
+struct ScalarArgs {
+  int tokens, heads, batch, out_f32;
+  float scale;
+  const __half *q, *k, *v;
+  long long q_ts, q_hs, q_bs;  // token / head / image strides, elements
+  long long k_ts, k_hs, k_bs;
+  long long v_ts, v_hs, v_bs;
+  const float* key_mask;
+  long long mask_batch_stride;
+  void* o;
+  long long o_tok_stride, o_head_stride, o_batch_stride;
+};
+
+int attn_fwd_smem_bytes();
+cudaError_t attn_fwd_configure();  // raises the kernel's dynamic shared-memory limit (once per device)
+cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
+                            const CUtensorMap& tm_v, const AttnArgs& args);
+cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args);
+// Classifies the K/V tiles of each image under `key_mask` and writes the tile lists
+// (1 + n_kv_tiles ints per image, `list_stride` ints apart).
+cudaError_t launch_mask_prepare(cudaStream_t stream, const float* key_mask, long long mask_batch_stride,
+                                int tokens, int batch, int* tile_list, long long list_stride);
+
+}  // namespace zdraw

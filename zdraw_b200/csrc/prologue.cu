@@ -1,0 +1,152 @@
+// Fused QK prologue: per-(token, head) RMSNorm with per-segment weights, pair-rotation
+// RoPE from per-token cos/sin tables, cast to fp16 — one pass over q and k, HBM-bound.
+//
+// Replaces the reference kernels krms_rope / krms_rope_hm
+// (src/klein/zflux2_glue_shader.zig:61-122), qk_norm_rope (src/metal/mqk_shader.zig:46-97)
+// and qk_norm_rope_hm_f16 (src/metal/metal_api.m:6201-6266); the layout/cast shims
+// to_headmajor_f16 (metal_api.m:6124-6145) are absorbed by the strided store.
+//
+// Math per row x[128] (f32 throughout, as the reference's GPU kernels):
+//   inv = 1 / sqrt(mean(x^2) + eps);  xn_j = x_j * inv * w_j
+//   y_2i = xn_2i * cos_2i - xn_2i+1 * sin_2i;  y_2i+1 = xn_2i+1 * cos_2i+1 + xn_2i * sin_2i+1
+//   store clamp(y, +-65504) as f16 (the reference clamps on every half store,
+//   zflux2_glue_shader.zig:119-120).
+//
+// Mapping: 16 lanes per row, 8 consecutive elements per lane (one 16-byte load for
+// f16 input, two for f32; one 16-byte store). The sum of squares is reduced with
+// xor shuffles in a fixed order, so results are bit-identical run to run.
+#include "prologue.cuh"
+
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace zdraw {
+
+namespace {
+
+constexpr int kRowsPerBlock = 16;  // 256 threads
+constexpr float kHalfMax = 65504.0f;
+
+__device__ __forceinline__ void load8(const __half* p, float* x) {
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    x[2 * i] = f.x;
+    x[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load8(const float* p, float* x) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+  x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+
+__device__ __forceinline__ uint32_t pack_clamped(float lo, float hi) {
+  lo = fminf(fmaxf(lo, -kHalfMax), kHalfMax);
+  hi = fminf(fmaxf(hi, -kHalfMax), kHalfMax);
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <typename TIn>
+__global__ void __launch_bounds__(kRowsPerBlock * 16)
+qk_norm_rope_kernel(const PrologueArgs a) {
+  const int which = blockIdx.y;  // 0 = q, 1 = k
+  const long long rows = static_cast<long long>(a.batch) * a.tokens * a.heads;
+  const long long row_raw = static_cast<long long>(blockIdx.x) * kRowsPerBlock + (threadIdx.x >> 4);
+  // Past the end: redo the last row and skip the store, so every lane reaches the shuffles.
+  const bool live = row_raw < rows;
+  const long long row = live ? row_raw : rows - 1;
+  const int sub = threadIdx.x & 15;
+  const int head = static_cast<int>(row % a.heads);
+  const long long bt = row / a.heads;
+  const int tok = static_cast<int>(bt % a.tokens);
+  const int img = static_cast<int>(bt / a.tokens);
+
+  const TIn* src = static_cast<const TIn*>(which ? a.k : a.q);
+  const long long ld = which ? a.ld_k : a.ld_q;
+  src += (static_cast<long long>(img) * a.tokens + tok) * ld + static_cast<long long>(head) * 128 + sub * 8;
+  float x[8];
+  load8(src, x);
+
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
+  // Lanes 0-15 and 16-31 of a warp hold different rows; offsets < 16 keep them apart.
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  const float inv = 1.0f / sqrtf(ss * (1.0f / 128.0f) + a.eps);
+
+  const float* w = (tok < a.txt_tokens) ? (which ? a.k_w_txt : a.q_w_txt) : (which ? a.k_w_img : a.q_w_img);
+  float wv[8], cv[8], sv[8];
+  load8(w + sub * 8, wv);
+  const long long rope_off = static_cast<long long>(img) * a.rope_batch_stride +
+                             static_cast<long long>(tok) * 128 + sub * 8;
+  load8(a.rope_cos + rope_off, cv);
+  load8(a.rope_sin + rope_off, sv);
+
+  uint32_t out[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float x0 = x[2 * i] * inv * wv[2 * i];
+    const float x1 = x[2 * i + 1] * inv * wv[2 * i + 1];
+    const float y0 = x0 * cv[2 * i] - x1 * sv[2 * i];
+    const float y1 = x1 * cv[2 * i + 1] + x0 * sv[2 * i + 1];
+    out[i] = pack_clamped(y0, y1);
+  }
+
+  __half* dst = static_cast<__half*>(which ? a.k_out : a.q_out);
+  long long off;
+  if (a.out_head_major) {
+    off = ((static_cast<long long>(img) * a.heads + head) * a.tokens + tok) * 128;
+  } else {
+    off = ((static_cast<long long>(img) * a.tokens + tok) * a.heads + head) * 128;
+  }
+  if (live) *reinterpret_cast<uint4*>(dst + off + sub * 8) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// f32 token-major (ld) -> f16 token-major dense; the cast the reference does in
+// to_headmajor_f16 for V (metal_api.m:6124-6145), without the transpose: the
+// attention kernel reads V through strides.
+__global__ void cast_f32_to_f16_kernel(const float* src, __half* dst, long long rows, int row_elems,
+                                       long long ld_src) {
+  const long long per_row = row_elems / 8;
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows * per_row) return;
+  const long long r = i / per_row;
+  const int c = static_cast<int>(i % per_row) * 8;
+  float x[8];
+  load8(src + r * ld_src + c, x);
+  uint32_t out[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) out[k] = pack_clamped(x[2 * k], x[2 * k + 1]);
+  *reinterpret_cast<uint4*>(dst + r * row_elems + c) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+}  // namespace
+
+cudaError_t launch_qk_norm_rope(cudaStream_t stream, const PrologueArgs& a, bool in_f32) {
+  const long long rows = static_cast<long long>(a.batch) * a.tokens * a.heads;
+  const dim3 grid(static_cast<unsigned>((rows + kRowsPerBlock - 1) / kRowsPerBlock), 2);
+  if (in_f32) {
+    qk_norm_rope_kernel<float><<<grid, kRowsPerBlock * 16, 0, stream>>>(a);
+  } else {
+    qk_norm_rope_kernel<__half><<<grid, kRowsPerBlock * 16, 0, stream>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cast_f32_to_f16(cudaStream_t stream, const float* src, void* dst, long long rows,
+                                   int row_elems, long long ld_src) {
+  const long long n = rows * (row_elems / 8);
+  const int threads = 256;
+  cast_f32_to_f16_kernel<<<static_cast<unsigned>((n + threads - 1) / threads), threads, 0, stream>>>(
+      src, static_cast<__half*>(dst), rows, row_elems, ld_src);
+  return cudaGetLastError();
+}
+
+}  // namespace zdraw
