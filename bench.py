@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Benchmark of the joint-attention hot path (QK RMSNorm + RoPE prologue, then flash attention).
+
+    python bench.py --gpus N --steps K --warmup W [--workload klein_1024] [--impl reference]
+
+One step = one pass of the hot path (``zdraw_cuda_joint_attention``) over one synthetic batch.
+At N GPUs every rank runs the same workload on its own image (seed): the path shards by
+(image, head) with no exchange step, so scaling is weak and no collective is on the data path.
+Rank 0 prints one JSON line.
+
+Timed regions (all on the device with CUDA events, after warm-up):
+  value      K back-to-back steps with inputs resident in HBM; max over ranks.
+  roofline   the attention kernel alone (prologue output reused), K launches: TFLOP/s against
+             the measured dense bf16 matmul peak.
+  prologue   the prologue kernel alone: GB/s against the measured HBM copy peak.
+  e2e        the same step through ``zdraw_cuda_joint_attention_host`` with pinned HOST buffers,
+             host->device and device->host copies inside the timed region.
+  cpu_baseline  the CPU oracle (a port of the reference's scalar CPU path) on a bounded sample of
+             query rows, on the host cores (rank 0, N = 1 only).
+
+Inputs rotate over several buffer sets whose total exceeds the L2 cache, so no step finds its
+inputs cached from the step before.
+
+``--impl reference`` times the reference's CPU implementation of the path (the oracle port: the
+reference itself is Zig + Metal and cannot be built on Linux) with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+NOMINAL_FP16_TFLOPS = 2250.0  # B200 dense fp16/bf16, nominal
+L2_BYTES = 126e6
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {k: float(d[k]) for k in FALLBACK_PEAKS if k in d} | {"source": "measured"}
+    return dict(FALLBACK_PEAKS) | {"source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while the timed regions run."""
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+class OracleTimer:
+    """Times the CPU oracle's joint attention on a range of query rows of one image.
+
+    A call costs `overhead` (the prologue over the whole sequence, paid once per call) plus
+    `per_row` seconds per query row (uniform for non-causal attention); a full call is
+    extrapolated as overhead + tokens * per_row.
+    """
+
+    def __init__(self, w):
+        import oracle
+        from zdraw_b200 import workloads
+
+        self.oracle = oracle
+        self.w = w.with_batch(1)
+        x = workloads.make_inputs(self.w, "cpu")
+        self.h = {k: (v.float().numpy() if v is not None else None) for k, v in x.items()}
+        self.norm_kind = 0 if w.family == "klein" else 1
+
+    def run(self, rows: int) -> float:
+        h, w = self.h, self.w
+        b0 = (w.tokens - rows) // 2
+        t0 = time.perf_counter()
+        self.oracle.joint_attention(h["q"][0], h["k"][0], h["v"][0], h["q_w_txt"], h["q_w_img"], h["k_w_txt"],
+                                    h["k_w_img"], h["rope_cos"], h["rope_sin"], w.heads, w.txt_tokens,
+                                    self.norm_kind, w.eps, key_mask=h["key_mask"], rows=(b0, b0 + rows))
+        return time.perf_counter() - t0
+
+    def calibrate(self):
+        self.run(4)  # first touch of the inputs
+        t_a, t_b = self.run(4), self.run(36)
+        per_row = max((t_b - t_a) / 32.0, 1e-6)
+        self.overhead = max(t_a - 4 * per_row, 0.0)
+        return per_row
+
+    def rows_for(self, seconds: float) -> int:
+        per_row = self.calibrate()
+        return int(max(8, min(self.w.tokens, seconds / per_row)))
+
+    def tflops(self, rows: int, dt: float) -> float:
+        per_row = max(dt - self.overhead, 1e-9) / rows
+        return self.w.flops / (self.overhead + self.w.tokens * per_row) / 1e12
+
+
+def run_reference(args, rank: int):
+    """The reference arm: the reference's CPU path (oracle port), all host threads, rank 0 only."""
+    if rank != 0:
+        return
+    import oracle
+    from zdraw_b200 import workloads
+
+    w = workloads.WORKLOADS[args.workload]
+    oracle.build()
+    cores = oracle.num_threads()
+    timer = OracleTimer(w)
+    # Size a step to about 2 s of CPU work, bounded so that the whole run stays within minutes.
+    budget = min(2.0, 120.0 / max(args.steps + args.warmup, 1))
+    rows = timer.rows_for(budget)
+    for _ in range(args.warmup):
+        timer.run(rows)
+    t_total, vals = 0.0, []
+    for _ in range(args.steps):
+        dt = timer.run(rows)
+        vals.append(timer.tflops(rows, dt))
+        t_total += dt
+    value = sum(vals) / len(vals)
+    sample = f"{rows} of {w.tokens} query rows x all {w.heads} heads of one image per step, all keys; extrapolated linearly in rows"
+    line = {
+        "impl": "reference", "metric": "attention TFLOP/s", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * w.with_batch(1).flops / (value * 1e12), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "batch": 1, "heads": w.heads, "tokens": w.tokens, "head_dim": 128,
+                   "note": "reference CPU path restated in C (oracle port); the reference itself is Zig + Metal"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="klein_1024")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU-baseline sample budget")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 20)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from zdraw_b200 import mattn, workloads
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for this path)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    w0 = workloads.WORKLOADS[args.workload]
+    # Each rank works on its own image(s): a different seed per rank.
+    from dataclasses import replace
+
+    w = replace(w0, seed=w0.seed + 1000 * rank)
+    ctx = mattn.Context(local_rank)
+    p = workloads.params(w)
+    ctx.reserve(p)
+
+    # Buffer sets: enough copies that one pass over all of them exceeds L2.
+    x0 = workloads.make_inputs(w, "cuda")
+    step_bytes = sum(x0[n].numel() * x0[n].element_size() for n in ("q", "k", "v")) * 4 // 3  # + o
+    n_sets = max(2, int(3 * L2_BYTES // step_bytes) + 1)
+    sets = [x0] + [{k: (v.clone() if (v is not None and k in ("q", "k", "v")) else v) for k, v in x0.items()}
+                   for _ in range(n_sets - 1)]
+    outs = [torch.empty((w.batch, w.tokens, w.heads, 128), dtype=x0["q"].dtype, device="cuda") for _ in range(n_sets)]
+    stream = torch.cuda.current_stream()
+
+    def step(i):
+        x = sets[i % n_sets]
+        ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                            x["rope_cos"], x["rope_sin"], outs[i % n_sets], p, key_mask=x["key_mask"], stream=stream)
+
+    launches_per_step = 2 + (1 if w.masked_text is not None else 0) + (1 if w.dtype == "f32" else 0)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    # ---- whole step, inputs resident
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    ev1.record(stream)
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    if ctx.last_status() != 0:
+        raise SystemExit("a kernel reported a non-zero status during the timed region")
+
+    # ---- attention kernel alone (dominant kernel) and prologue alone
+    q16 = [torch.empty((w.batch, w.heads, w.tokens, 128), dtype=torch.float16, device="cuda") for _ in range(n_sets)]
+    k16 = [torch.empty_like(q16[0]) for _ in range(n_sets)]
+
+    def prologue(i):
+        x = sets[i % n_sets]
+        ctx.qk_norm_rope(x["q"], x["k"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"], x["rope_cos"],
+                         x["rope_sin"], q16[i % n_sets], k16[i % n_sets], p, stream=stream)
+
+    def attention(i):
+        x = sets[i % n_sets]
+        ctx.run_on_handles(q16[i % n_sets], k16[i % n_sets], x["v"], outs[i % n_sets], p, key_mask=x["key_mask"],
+                           stream=stream)
+
+    def timed(fn):
+        for i in range(max(3, args.warmup)):
+            fn(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for i in range(args.steps):
+            fn(i)
+        b.record(stream)
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps
+
+    ms_prologue = timed(prologue)
+    ms_attention = timed(attention)
+
+    # ---- end to end from pinned host buffers through the host-buffer C-ABI entry point
+    xh = workloads.make_inputs(w, "cpu", pin=True)
+    oh = torch.empty((w.batch, w.tokens, w.heads, 128), dtype=xh["q"].dtype).pin_memory()
+    h2d = sum(xh[n].numel() * xh[n].element_size() for n in xh if xh[n] is not None)
+    d2h = oh.numel() * oh.element_size()
+    e2e_steps = args.e2e_steps or min(args.steps, 20)
+
+    def e2e_step():
+        ctx.joint_attention_host(xh["q"], xh["k"], xh["v"], xh["q_w_txt"], xh["q_w_img"], xh["k_w_txt"],
+                                 xh["k_w_img"], xh["rope_cos"], xh["rope_sin"], oh, p, key_mask=xh["key_mask"])
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()  # returns when the result is on the host
+    t_e2e = (time.perf_counter() - t0) / e2e_steps
+    barrier()
+    clocks = sampler.stop()
+
+    # ---- max over ranks
+    times = torch.tensor([ms_total, ms_prologue, ms_attention, t_e2e * 1e3], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_prologue, ms_attention, ms_e2e = times.tolist()
+
+    flops_rank = w.flops
+    ms_step = ms_total / args.steps
+    value = world * flops_rank / (ms_step * 1e-3) / 1e12
+    attn_tflops = flops_rank / (ms_attention * 1e-3) / 1e12
+    e2e_value = world * flops_rank / (ms_e2e * 1e-3) / 1e12
+    in_size = 4 if w.dtype == "f32" else 2
+    elems = w.batch * w.tokens * w.heads * 128
+    prologue_bytes = 2 * elems * in_size + 2 * elems * 2 + 2 * w.tokens * 128 * 4
+    prologue_gbs = prologue_bytes / (ms_prologue * 1e-3) / 1e9
+
+    if rank == 0:
+        peaks = measured_peaks()
+        line = {
+            "metric": "attention TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)", "data": "synthetic",
+            "config": {
+                "workload": w.name, "batch_per_gpu": w.batch, "heads": w.heads, "tokens": w.tokens, "head_dim": 128,
+                "flops_per_step_per_gpu": flops_rank, "step": "qk_norm_rope prologue + attention (joint call)",
+                "sharding": "one image (seed) per GPU, no collective",
+                "l2": f"inputs rotate over {n_sets} buffer sets ({n_sets * step_bytes / 1e6:.0f} MB > 126 MB L2)",
+            },
+            "roofline": {
+                "kernel": "attn_fwd_kernel", "bound": "tensor", "achieved": attn_tflops,
+                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": attn_tflops / peaks["bf16_tflops"],
+                "peak_source": peaks["source"] + " dense bf16 matmul, burst",
+                "frac_of_sustained": attn_tflops / peaks["bf16_tflops_sustained"],
+                "frac_of_nominal_fp16": attn_tflops / NOMINAL_FP16_TFLOPS,
+                "ms_per_launch": ms_attention, "traffic": None,
+            },
+            "prologue": {"kernel": "qk_norm_rope_kernel", "bound": "hbm", "achieved": prologue_gbs,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": prologue_gbs / peaks["hbm_gbs"],
+                         "ms_per_launch": ms_prologue, "algorithmic_bytes": prologue_bytes},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e, "steps": e2e_steps,
+                    "api": "zdraw_cuda_joint_attention_host (pinned host buffers)"},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            import oracle
+
+            oracle.build()
+            timer = OracleTimer(w)
+            rows = timer.rows_for(args.cpu_seconds)
+            dt = timer.run(rows)
+            v = timer.tflops(rows, dt)
+            line["cpu_baseline"] = {
+                "value": v, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+                "sample": f"{rows} of {w.tokens} query rows x all {w.heads} heads, all keys, {dt:.1f} s; "
+                          "work per row is uniform, extrapolated linearly",
+            }
+        print(json.dumps(line), flush=True)
+
+    ctx.deinit()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -47,10 +47,14 @@ constexpr int kHalfBytes = 16384;  // 128 rows x 64 f16: one 128B-swizzled block
 constexpr int kThreads = 384;
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 constexpr float kRescaleThreshold = 8.0f;                       // log2 units
-// Register budgets after setmaxnreg: per SM sub-partition one warp of each warpgroup is
-// resident, and 80 + 216 + 216 = 512 (= 16384 registers / 32 lanes).
-constexpr int kRegsControl = 80;
-constexpr int kRegsSoftmax = 216;
+// Register budgets after setmaxnreg. The CTA is launched with 168 registers per thread
+// (3 warpgroups x 168 = 504 per lane triple); what the control warpgroup gives up is all the
+// softmax warpgroups can take, so kRegsControl + 2 * kRegsSoftmax must not exceed 504
+// (an increase beyond the CTA's pool would wait forever).
+constexpr int kRegsControl = 88;
+constexpr int kRegsSoftmax = 208;
+static_assert(kRegsControl + 2 * kRegsSoftmax <= 3 * 168, "setmaxnreg budget");
+static_assert(kRegsControl % 8 == 0 && kRegsSoftmax % 8 == 0, "setmaxnreg granularity");
 
 // Shared-memory carve-up (offsets from a 1024-byte aligned base).
 constexpr int kOffQ = 0;
@@ -536,6 +540,12 @@ __global__ void mask_prepare_kernel(const float* key_mask, long long mask_batch_
 int attn_fwd_smem_bytes() { return kSmemBytes; }
 
 cudaError_t attn_fwd_configure() {
+  // The setmaxnreg budgets assume the registers the CTA is launched with; refuse to run a build
+  // whose register count would let an increase wait forever.
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, attn_fwd_kernel);
+  if (e != cudaSuccess) return e;
+  if (3 * attr.numRegs < kRegsControl + 2 * kRegsSoftmax) return cudaErrorInvalidConfiguration;
   return cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
