@@ -1,0 +1,108 @@
+//! Zig declarations of the CUDA joint-attention C ABI (include/zdraw_cuda.h), in the style
+//! of the reference's src/metal/metal_c.zig. Written for Zig 0.16; it has NOT been compiled
+//! (no Zig toolchain was available where this repository was built) — compile it where
+//! `zig` exists and keep the comptime size assert.
+
+pub const ok: c_int = 0;
+pub const declined: c_int = 1; // shape outside the kernels; nothing enqueued (error.UnsupportedShape)
+pub const dtype_f16: u32 = 1;
+pub const dtype_f32: u32 = 3;
+pub const layout_token_major: u32 = 0;
+pub const layout_head_major: u32 = 1;
+
+pub const AttnParams = extern struct {
+    batch: u32,
+    tokens: u32,
+    heads: u32,
+    head_dim: u32,
+    txt_tokens: u32,
+    in_dtype: u32,
+    out_dtype: u32,
+    out_layout: u32 = layout_token_major,
+    qk_layout: u32 = layout_head_major,
+    has_key_mask: u32 = 0,
+    kernel: u32 = 0,
+    reserved: u32 = 0,
+    norm_eps: f32,
+    softmax_scale: f32 = 0.0,
+    ld_q: u64 = 0,
+    ld_k: u64 = 0,
+    ld_v: u64 = 0,
+    ld_o: u64 = 0,
+    mask_batch_stride: u64 = 0,
+    rope_batch_stride: u64 = 0,
+};
+
+comptime {
+    // Same role as src/runtime/abi_assert.zig:25-41.
+    if (@sizeOf(AttnParams) != 104) @compileError("zdraw_cuda_attn_params size drifted");
+}
+
+pub extern fn zdraw_cuda_attn_params_size() usize;
+pub extern fn zdraw_cuda_attn_create(device: c_int, ctx: *?*anyopaque) c_int;
+pub extern fn zdraw_cuda_attn_destroy(ctx: *anyopaque) c_int;
+pub extern fn zdraw_cuda_attn_reserve(ctx: *anyopaque, params: *const AttnParams) c_int;
+pub extern fn zdraw_cuda_qk_norm_rope(
+    ctx: *anyopaque,
+    stream: ?*anyopaque,
+    q: *const anyopaque,
+    k: *const anyopaque,
+    q_w_txt: [*]const f32,
+    q_w_img: [*]const f32,
+    k_w_txt: [*]const f32,
+    k_w_img: [*]const f32,
+    rope_cos: [*]const f32,
+    rope_sin: [*]const f32,
+    q_out_f16: *anyopaque,
+    k_out_f16: *anyopaque,
+    params: *const AttnParams,
+) c_int;
+pub extern fn zdraw_cuda_attention(
+    ctx: *anyopaque,
+    stream: ?*anyopaque,
+    q_f16: *const anyopaque,
+    k_f16: *const anyopaque,
+    v: *const anyopaque,
+    key_mask: ?[*]const f32,
+    o: *anyopaque,
+    params: *const AttnParams,
+) c_int;
+pub extern fn zdraw_cuda_joint_attention(
+    ctx: *anyopaque,
+    stream: ?*anyopaque,
+    q: *const anyopaque,
+    k: *const anyopaque,
+    v: *const anyopaque,
+    q_w_txt: [*]const f32,
+    q_w_img: [*]const f32,
+    k_w_txt: [*]const f32,
+    k_w_img: [*]const f32,
+    rope_cos: [*]const f32,
+    rope_sin: [*]const f32,
+    key_mask: ?[*]const f32,
+    o: *anyopaque,
+    params: *const AttnParams,
+) c_int;
+pub extern fn zdraw_cuda_last_status(ctx: *anyopaque, stream: ?*anyopaque, status: *u32) c_int;
+pub extern fn zdraw_cuda_last_error(ctx: ?*anyopaque) [*:0]const u8;
+pub extern fn zdraw_cuda_klein_rope_table(
+    cos_out: [*]f32,
+    sin_out: [*]f32,
+    txt_len: usize,
+    grid_h: usize,
+    grid_w: usize,
+    ref_h: usize,
+    ref_w: usize,
+    theta: f64,
+) c_int;
+
+pub const Error = error{ UnsupportedShape, InvalidShape, CudaFailed };
+
+pub fn check(code: c_int) Error!void {
+    return switch (code) {
+        0 => {},
+        1 => error.UnsupportedShape,
+        -1 => error.InvalidShape,
+        else => error.CudaFailed,
+    };
+}

@@ -1,0 +1,52 @@
+"""Runs the joint-attention path a few times on one synthetic workload (for profilers).
+
+    python -m zdraw_b200.profile_case --workload klein_1024 --iters 4
+
+One untimed call, then `iters` timed ones. Launches per call: qk_norm_rope_kernel, attn_fwd_kernel (plus mask_prepare_kernel with a key
+mask and cast_f32_to_f16_kernel for f32 inputs). Prints the mean device time per iteration.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import mattn, workloads
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="klein_1024", choices=sorted(workloads.WORKLOADS))
+    ap.add_argument("--iters", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch")
+    args = ap.parse_args()
+    w = workloads.WORKLOADS[args.workload]
+    if args.batch:
+        w = w.with_batch(args.batch)
+    torch.cuda.set_device(0)
+    ctx = mattn.Context(0)
+    x = workloads.make_inputs(w, "cuda")
+    p = workloads.params(w)
+    out = torch.empty((w.batch, w.tokens, w.heads, 128), dtype=x["q"].dtype, device="cuda")
+    def call():
+        ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                            x["rope_cos"], x["rope_sin"], out, p, key_mask=x["key_mask"])
+
+    call()  # first call sizes the context scratch
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.iters):
+        call()
+    e1.record()
+    torch.cuda.synchronize()
+    status = ctx.last_status()
+    ms = e0.elapsed_time(e1) / args.iters
+    print(f"{w.name}: {ms:.4f} ms/iter, {w.flops / ms / 1e9:.1f} TFLOP/s, status {status}")
+    ctx.deinit()
+    if status != 0:
+        raise SystemExit(1)
+
+
+if __name__ == "__main__":
+    main()
