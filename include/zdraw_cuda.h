@@ -172,6 +172,34 @@ ZDRAW_CUDA_API int zdraw_cuda_joint_attention_host(void *ctx, const void *q, con
                                     const zdraw_cuda_attn_params *p);
 
 /*
+ * The joint call for callers that cannot allocate device memory when they need attention
+ * (a render loop whose memory was all reserved up front, a plugin held to a fixed device-memory
+ * budget by its host, a process told that an allocation may stall the GPU it shares).
+ * It has no counterpart in the reference: the reference's scratch slots always grow on demand.
+ *
+ * Same arguments and results as zdraw_cuda_joint_attention, but no context: the fp16 q/k
+ * between prologue and attention live in a fixed 64 MiB array inside the library's device
+ * image, so the call never calls cudaMalloc/cudaFree or any allocating routine.
+ *   - Limit: 2 * batch * heads * tokens * 128 * 2 bytes <= 64 MiB (one 1024x1024 Klein call is
+ *     54 MiB). Larger calls, f32 inputs, a key mask or the scalar kernel are refused with
+ *     ZDRAW_CUDA_DECLINED and nothing is enqueued. Every GPU that loads this part of the
+ *     library holds the 64 MiB until the process exits.
+ *   - The CUDA device of `stream` must be current. The first call on a device looks up the
+ *     array's device address (cudaGetSymbolAddress) and configures the kernel; make that first
+ *     call before starting any stream capture.
+ *   - All calls share the one array and one status word (cleared on the stream at the start of
+ *     each call): calls that overlap on the GPU race. Keep them on one stream or order them.
+ *   - `error_text`, if not NULL, receives a static string describing a refusal or failure.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_joint_attention_static(void *stream, const void *q, const void *k,
+                                                     const void *v, const float *q_w_txt,
+                                                     const float *q_w_img, const float *k_w_txt,
+                                                     const float *k_w_img, const float *rope_cos,
+                                                     const float *rope_sin, void *o,
+                                                     const zdraw_cuda_attn_params *p,
+                                                     const char **error_text);
+
+/*
  * Attention alone with HOST buffers (no prologue): q, k, v in in_dtype, token-major;
  * f32 q/k/v are cast to fp16 on the device first. This is the call shape of
  * mattn.Context.run (src/metal/mattn.zig:152-173: out, q, k, v slices + Config),
