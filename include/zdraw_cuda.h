@@ -238,6 +238,15 @@ ZDRAW_CUDA_API int zdraw_cuda_zimage_rope_table(float *cos_out, float *sin_out, 
  */
 ZDRAW_CUDA_API int zdraw_cuda_last_status(void *ctx, void *stream, uint32_t *device_status);
 
+/*
+ * Debugging aid, the counterpart of ZDRAW_KLEIN_TRACE's per-stage GPU times
+ * (src/klein/zflux2_resident.zig:380-409): while a device buffer of at least 1600 64-bit words is
+ * set, the first CTA of every attention launch writes clock stamps of its pipeline events
+ * ([role 0 = MMA, 1/2 = softmax tile 0/1, 3 = TMA producer, 4 = MMA operand waits][K/V step < 40][event < 8]) into it and the launch uses
+ * an instrumented copy of the kernel. NULL switches it off (the default).
+ */
+ZDRAW_CUDA_API int zdraw_cuda_attn_set_trace(void *ctx, void *device_words, size_t n_words);
+
 /* Human-readable text of the last failure on this context (never NULL). */
 ZDRAW_CUDA_API const char *zdraw_cuda_last_error(void *ctx);
 

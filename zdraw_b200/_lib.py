@@ -10,7 +10,8 @@ import os
 import subprocess
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libzdraw_cuda.so")
+# ZDRAW_CUDA_LIB selects another build of the same library (kernel tuning experiments).
+LIB_PATH = os.environ.get("ZDRAW_CUDA_LIB") or os.path.join(_HERE, "lib", "libzdraw_cuda.so")
 CSRC_DIR = os.path.join(_HERE, "csrc")
 
 OK, DECLINED, E_ARG, E_CUDA, E_DEVICE = 0, 1, -1, -2, -3
@@ -63,6 +64,7 @@ SYMBOLS = {
     "zdraw_cuda_klein_rope_table": (C.c_int, [_VP, _VP] + [C.c_size_t] * 5 + [C.c_double]),
     "zdraw_cuda_zimage_rope_table": (C.c_int, [_VP, _VP] + [C.c_size_t] * 3 + [_VP, _VP, C.c_float]),
     "zdraw_cuda_last_status": (C.c_int, [_VP, _VP, C.POINTER(C.c_uint32)]),
+    "zdraw_cuda_attn_set_trace": (C.c_int, [_VP, _VP, C.c_size_t]),
     "zdraw_cuda_last_error": (C.c_char_p, [_VP]),
 }
 

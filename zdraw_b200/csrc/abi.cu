@@ -41,6 +41,7 @@ struct Ctx {
   uint32_t* d_status = nullptr;
   EncodeTiledFn encode = nullptr;
   cudaStream_t host_stream = nullptr;  // used by the host-buffer entry point only
+  unsigned long long* d_trace = nullptr;  // caller's trace buffer while pipeline tracing is on (debugging)
   // Grow-only scratch (device memory).
   Buf q16, k16, v16, tile_list;
   Buf st_q, st_k, st_v, st_o, st_w, st_cos, st_sin, st_mask;  // staging for the host-buffer path
@@ -309,6 +310,7 @@ int run_attention(Ctx* c, cudaStream_t stream, const void* q16, const void* k16,
   a.o_head_stride = o_head;
   a.o_batch_stride = o_batch;
   a.status = c->d_status;
+  a.trace = c->d_trace;
   ZD_CUDA(c, zdraw::launch_attn_fwd(stream, tm_q, tm_k, tm_v, a));
   return ZDRAW_CUDA_OK;
 }
@@ -537,6 +539,15 @@ int zdraw_cuda_last_status(void* ctx, void* stream, uint32_t* device_status) {
   ZD_CUDA(c, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   ZD_CUDA(c, cudaMemcpy(device_status, c->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
   if (*device_status != 0) ZD_CUDA(c, cudaMemset(c->d_status, 0, sizeof(uint32_t)));
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_attn_set_trace(void* ctx, void* device_words, size_t n_words) {
+  Ctx* c = as_ctx(ctx);
+  if (!c) return ZDRAW_CUDA_E_ARG;
+  if (device_words != nullptr && n_words < static_cast<size_t>(zdraw::attn_fwd_trace_words()))
+    return fail(c, ZDRAW_CUDA_E_ARG, "trace buffer needs %d 64-bit words", zdraw::attn_fwd_trace_words());
+  c->d_trace = static_cast<unsigned long long*>(device_words);
   return ZDRAW_CUDA_OK;
 }
 

@@ -33,6 +33,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <type_traits>
+
 #include "ptx.cuh"
 
 namespace zdraw {
@@ -47,6 +49,8 @@ constexpr int kHalfBytes = 16384;  // 128 rows x 64 f16: one 128B-swizzled block
 constexpr int kThreads = 384;
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 constexpr float kRescaleThreshold = 8.0f;                       // log2 units
+constexpr int kTraceIters = 40, kTraceEvents = 8;
+constexpr int kEmuPairsOf4 = 1;  // of every 4 score pairs, how many take the FMA-pipe exp2 (0..4)
 // Register budgets after setmaxnreg. The CTA is launched with 168 registers per thread
 // (3 warpgroups x 168 = 504 per lane triple); what the control warpgroup gives up is all the
 // softmax warpgroups can take, so kRegsControl + 2 * kRegsSoftmax must not exceed 504
@@ -65,10 +69,10 @@ constexpr int kBarQFull = 0;                      // [2]
 constexpr int kBarKVFull = 2;                     // [kStages]
 constexpr int kBarKVEmpty = 2 + kStages;          // [kStages]
 constexpr int kBarSFull = 2 + 2 * kStages;        // [2]
-constexpr int kBarPFull = 4 + 2 * kStages;        // [2]
-constexpr int kBarOFull = 6 + 2 * kStages;        // [2]
-constexpr int kBarDrain = 8 + 2 * kStages;        // [1]
-constexpr int kNumBars = 9 + 2 * kStages;
+constexpr int kBarPFull = 4 + 2 * kStages;        // [2 tiles][2 key halves]
+constexpr int kBarOFull = 8 + 2 * kStages;        // [2]
+constexpr int kBarDrain = 10 + 2 * kStages;       // [1]
+constexpr int kNumBars = 11 + 2 * kStages;
 constexpr int kOffFlags = kOffBar + kNumBars * 8;  // u32 abort, u32 tmem base
 constexpr int kSmemBytes = kOffFlags + 16 + 1024;  // + alignment slack
 
@@ -99,6 +103,30 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   }
 }
 
+// 2^x for a packed pair on the FMA pipe. x is clamped to >= -126 so the exponent arithmetic
+// cannot wrap; x <= 8 + small by construction (lazy rescale threshold). Relative error of the
+// cubic on [-0.5, 0.5] is 7.5e-5, below the fp16 rounding of P (4.9e-4).
+__device__ __forceinline__ uint64_t exp2_emulated_pair(uint64_t x2) {
+  float x0, x1;
+  f2_unpack(x2, x0, x1);
+  x0 = fmaxf(x0, -126.0f);
+  x1 = fmaxf(x1, -126.0f);
+  const uint64_t xc = f2_pack(x0, x1);
+  const uint64_t magic = f2_pack(12582912.0f, 12582912.0f);  // 1.5 * 2^23: x + magic rounds x to an integer
+  const uint64_t t2 = f2_add(xc, magic);
+  const uint64_t r2 = f2_sub(xc, f2_sub(t2, magic));
+  uint64_t p2 = f2_fma(r2, f2_pack(0.0551716648f, 0.0551716648f), f2_pack(0.2426111251f, 0.2426111251f));
+  p2 = f2_fma(p2, r2, f2_pack(0.6932609677f, 0.6932609677f));
+  p2 = f2_fma(p2, r2, f2_pack(0.9999280572f, 0.9999280572f));
+  float p0, p1, t0, t1;
+  f2_unpack(p2, p0, p1);
+  f2_unpack(t2, t0, t1);
+  // The low mantissa bits of t hold round(x) in two's complement: shift them onto the exponent.
+  p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+  return f2_pack(p0, p1);
+}
+
 __device__ __forceinline__ void store_row_chunk(const AttnArgs& a, size_t row_off, int col,
                                                 const float* v) {
   // 32 consecutive output columns of one row, starting at `col`.
@@ -120,6 +148,9 @@ __device__ __forceinline__ void store_row_chunk(const AttnArgs& a, size_t row_of
   }
 }
 
+// kTrace: CTA (0,0,0) writes clock64() stamps of its pipeline events for the first
+// kTraceIters K/V steps to a.trace (a debugging aid; the product launch uses kTrace = false).
+template <bool kTrace>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnArgs a) {
@@ -133,6 +164,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const bool tracing = kTrace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  auto stamp = [&](int role, int step, int event) {
+    if (kTrace && tracing && step < kTraceIters)
+      a.trace[(role * kTraceIters + step) * kTraceEvents + event] = static_cast<unsigned long long>(clock64());
+  };
   const int q_tile0 = blockIdx.x * 2;
   const int head = blockIdx.y;
   const int img = blockIdx.z;
@@ -149,7 +185,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar(kBarSFull + t), 1);
-      mbar_init(bar(kBarPFull + t), kBM);
+      mbar_init(bar(kBarPFull + 2 * t), kBM);
+      mbar_init(bar(kBarPFull + 2 * t + 1), kBM);
       mbar_init(bar(kBarOFull + t), 1);
     }
     mbar_init(bar(kBarDrain), 1);
@@ -200,8 +237,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           for (int which = 0; which < 2; ++which, ++it) {
             const uint32_t stage = it % kStages;
             const uint32_t phase = (it / kStages) & 1u;
+            stamp(3, jj, 2 * which);
             ok = wait_bar(bar(kBarKVEmpty + stage), phase ^ 1u, abort_flag, a.status, kStProducer);
             if (!ok) break;
+            stamp(3, jj, 2 * which + 1);
             const uint32_t dst = base + kOffKV + stage * kTileBytes;
             const CUtensorMap* tm = which ? &tm_v : &tm_k;
             const int hm = which ? a.v_head_major : a.k_head_major;
@@ -236,12 +275,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         };
         // O_t (+)= P_t V: the K dimension is 128 keys = 8 steps of 16 keys (2048 bytes of V
         // rows, 8 TMEM columns of packed f16 P); N = head_dim spans two 64-column blocks (LBO).
-        auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate) {
+        // `half` selects keys [0,64) or [64,128) of the tile: the softmax warps hand P over in two
+        // pieces so that the first four MMAs run while the second half is still being exponentiated.
+        auto issue_pv = [&](int t, uint32_t v_addr, int half, bool accumulate) {
           const uint64_t desc_v = smem_desc_sw128(v_addr, kHalfBytes, 1024);
           const uint32_t p_tmem = tmem_base + 128u * t;
           const uint32_t d_tmem = tmem_base + 256u + 128u * t;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
+          for (int kk = 0; kk < 4; ++kk) {
+            const int k = 4 * half + kk;
             umma_ts(d_tmem, p_tmem + 8u * k, desc_v + ((2048u * k) >> 4), idesc_pv,
                     (accumulate || k > 0) ? 1u : 0u);
           }
@@ -265,8 +307,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const uint32_t sv = it % kStages;
           const uint32_t phv = (it / kStages) & 1u;
           ++it;
+          stamp(4, jj, 0);
           ok = wait_bar(bar(kBarKVFull + sv), phv, abort_flag, a.status, kStMma);
           if (!ok) break;
+          stamp(4, jj, 1);
           const bool has_next = (jj + 1 < n_act);
           uint32_t sk = 0;
           if (has_next) {
@@ -276,21 +320,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ok = wait_bar(bar(kBarKVFull + sk), phk, abort_flag, a.status, kStMma);
             if (!ok) break;
           }
+          stamp(4, jj, 2);
           tc_fence_after();
           const uint32_t v_addr = base + kOffKV + sv * kTileBytes;
           const uint32_t k_addr = base + kOffKV + sk * kTileBytes;
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
-            ok = wait_bar(bar(kBarPFull + t), static_cast<uint32_t>(jj) & 1u, abort_flag, a.status, kStMma);
+            stamp(0, jj, 4 * t + 0);
+            ok = wait_bar(bar(kBarPFull + 2 * t), static_cast<uint32_t>(jj) & 1u, abort_flag, a.status, kStMma);
             if (!ok) break;
             tc_fence_after();
-            issue_pv(t, v_addr, jj > 0);
+            stamp(0, jj, 4 * t + 1);
+            issue_pv(t, v_addr, 0, jj > 0);
+            ok = wait_bar(bar(kBarPFull + 2 * t + 1), static_cast<uint32_t>(jj) & 1u, abort_flag, a.status, kStMma);
+            if (!ok) break;
+            tc_fence_after();
+            stamp(0, jj, 4 * t + 2);
+            issue_pv(t, v_addr, 1, jj > 0);
             if (has_next) {
               issue_qk(t, k_addr);
               umma_commit(bar(kBarSFull + t));
             } else {
               umma_commit(bar(kBarOFull + t));
             }
+            stamp(0, jj, 4 * t + 3);
           }
           if (!ok) break;
           umma_commit(bar(kBarKVEmpty + sv));
@@ -327,10 +380,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int jj = 0; jj < n_act; ++jj) {
       const int entry = tile_entry(jj);
       const int tile = entry & kTileIndexMask;
+      const bool tr = (quarter == 0 && lane == 0);
+      if (tr) stamp(1 + t, jj, 0);
       ok = __all_sync(0xffffffffu,
                       wait_bar(bar(kBarSFull + t), static_cast<uint32_t>(jj) & 1u, abort_flag, a.status, kStSoftmax));
       if (!ok) break;
       tc_fence_after();
+      if (tr) stamp(1 + t, jj, 1);
 
       if (entry & kTileMixedFlag) {
         // A tile the key mask covers partly (rare): add the mask, and -inf beyond the last
@@ -359,21 +415,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_x32(t_s + 96, sr + 96);
       tmem_wait_ld();
       float* s = reinterpret_cast<float*>(sr);
+      if (tr) stamp(1 + t, jj, 2);
 
       if (tile_list == nullptr && tile == last_tile && tail < kBN) {
 #pragma unroll
         for (int i = 0; i < 128; ++i) s[i] = (i < tail) ? s[i] : -INFINITY;
       }
 
-      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+      float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+      float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-      for (int i = 4; i < 128; i += 4) {
-        mx0 = fmaxf(mx0, s[i]);
-        mx1 = fmaxf(mx1, s[i + 1]);
-        mx2 = fmaxf(mx2, s[i + 2]);
-        mx3 = fmaxf(mx3, s[i + 3]);
+      for (int i = 12; i < 124; i += 8) {
+        mx0 = max3(mx0, s[i], s[i + 1]);
+        mx1 = max3(mx1, s[i + 2], s[i + 3]);
+        mx2 = max3(mx2, s[i + 4], s[i + 5]);
+        mx3 = max3(mx3, s[i + 6], s[i + 7]);
       }
-      const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+      mx0 = max3(mx0, s[124], s[125]);
+      mx1 = max3(mx1, s[126], s[127]);
+      const float m_new = max3(m, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 
       if (jj == 0) {
         m = m_new;
@@ -400,25 +460,59 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
 
+      if (tr) stamp(1 + t, jj, 3);
       const float mc = (m == -INFINITY) ? 0.0f : m * c;
-      float sum0 = 0.0f, sum1 = 0.0f;
+      // p = exp2(s*c - m*c) on pairs. Of every four pairs, kEmuPairsOf4 are evaluated on the FMA
+      // pipe (round-to-nearest split x = n + r, |r| <= 0.5, cubic for 2^r, n added to the
+      // exponent), the rest with MUFU ex2: the MUFU rate (16/clk/SM) would otherwise bound the
+      // kernel. Tiles that can hold -inf scores (masked or ragged) use MUFU for every element.
+      const bool plain = (entry & kTileMixedFlag) != 0 || (tile_list == nullptr && tile == last_tile && tail < kBN);
+      const uint64_t c2 = f2_pack(c, c);
+      const uint64_t nmc2 = f2_pack(-mc, -mc);
+      uint64_t acc0 = 0ull, acc1 = 0ull;  // packed partial row sums (+0.0f, +0.0f)
+      auto exp_phase = [&](auto emu_tag) {
+        constexpr int kEmu = decltype(emu_tag)::value;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t pk[16];
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2_approx(fmaf(s[32 * ch + 2 * i], c, -mc));
-          const float p1 = ex2_approx(fmaf(s[32 * ch + 2 * i + 1], c, -mc));
-          sum0 += p0;
-          sum1 += p1;
-          pk[i] = pack_f16x2(p0, p1);
+          for (int i = 0; i < 16; ++i) {
+            const int e = 32 * ch + 2 * i;
+            const uint64_t x2 = f2_fma(f2_pack(s[e], s[e + 1]), c2, nmc2);
+            uint64_t p2;
+            if ((i & 3) < kEmu) {
+              p2 = exp2_emulated_pair(x2);
+            } else {
+              float x0, x1;
+              f2_unpack(x2, x0, x1);
+              p2 = f2_pack(ex2_approx(x0), ex2_approx(x1));
+            }
+            if (i & 1) acc1 = f2_add(acc1, p2); else acc0 = f2_add(acc0, p2);
+            float p0, p1;
+            f2_unpack(p2, p0, p1);
+            pk[i] = pack_f16x2(p0, p1);
+          }
+          tmem_st_x16(t_s + 16u * ch, pk);
+          if (ch == 1 || ch == 3) {
+            // Keys [0,64) then [64,128) of P are handed to the MMA warp separately.
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(kBarPFull + 2 * t + (ch >> 1)));
+            if (tr) stamp(1 + t, jj, 4 + (ch >> 1));
+          }
         }
-        tmem_st_x16(t_s + 16u * ch, pk);
+      };
+      if (plain) {
+        exp_phase(std::integral_constant<int, 0>{});
+      } else {
+        exp_phase(std::integral_constant<int, kEmuPairsOf4>{});
       }
-      l += sum0 + sum1;
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar(kBarPFull + t));
+      {
+        float a0, a1, b0, b1;
+        f2_unpack(acc0, a0, a1);
+        f2_unpack(acc1, b0, b1);
+        l += (a0 + a1) + (b0 + b1);
+      }
     }
 
     if (ok && n_act > 0)
@@ -539,21 +633,32 @@ __global__ void mask_prepare_kernel(const float* key_mask, long long mask_batch_
 
 int attn_fwd_smem_bytes() { return kSmemBytes; }
 
+int attn_fwd_trace_words() { return 5 * kTraceIters * kTraceEvents; }
+
 cudaError_t attn_fwd_configure() {
   // The setmaxnreg budgets assume the registers the CTA is launched with; refuse to run a build
   // whose register count would let an increase wait forever.
   cudaFuncAttributes attr;
-  cudaError_t e = cudaFuncGetAttributes(&attr, attn_fwd_kernel);
+  cudaError_t e = cudaFuncGetAttributes(&attr, attn_fwd_kernel<false>);
   if (e != cudaSuccess) return e;
   if (3 * attr.numRegs < kRegsControl + 2 * kRegsSoftmax) return cudaErrorInvalidConfiguration;
-  return cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  e = cudaFuncGetAttributes(&attr, attn_fwd_kernel<true>);
+  if (e != cudaSuccess) return e;
+  if (3 * attr.numRegs < kRegsControl + 2 * kRegsSoftmax) return cudaErrorInvalidConfiguration;
+  e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
 cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
                             const CUtensorMap& tm_v, const AttnArgs& args) {
   const int n_q_tiles = (args.tokens + kBM - 1) / kBM;
   dim3 grid((n_q_tiles + 1) / 2, args.heads, args.batch);
-  attn_fwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, args);
+  if (args.trace != nullptr) {
+    attn_fwd_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, args);
+  } else {
+    attn_fwd_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, args);
+  }
   return cudaGetLastError();
 }
 

@@ -33,6 +33,7 @@ struct AttnArgs {
   void* o;
   long long o_tok_stride, o_head_stride, o_batch_stride;  // elements
   uint32_t* status;  // device status word
+  unsigned long long* trace;  // nullptr, or attn_fwd_trace_words() words for pipeline time stamps (debugging)
 };
 
 struct ScalarArgs {
@@ -49,6 +50,7 @@ struct ScalarArgs {
 };
 
 int attn_fwd_smem_bytes();
+int attn_fwd_trace_words();
 cudaError_t attn_fwd_configure();  // raises the kernel's dynamic shared-memory limit (once per device)
 cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
                             const CUtensorMap& tm_v, const AttnArgs& args);

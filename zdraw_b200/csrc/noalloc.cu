@@ -229,6 +229,7 @@ int zdraw_cuda_joint_attention_static(void* stream, const void* q, const void* k
   a.o_head_stride = o_hm ? static_cast<long long>(tokens) * kHeadDim : kHeadDim;
   a.o_batch_stride = o_hm ? static_cast<long long>(heads) * tokens * kHeadDim : static_cast<long long>(tokens) * ld_o;
   a.status = st->status;
+  a.trace = nullptr;
   if (zdraw::launch_attn_fwd(s, tm_q, tm_k, tm_v, a) != cudaSuccess) return fail(ZDRAW_CUDA_E_CUDA, "attention launch failed");
   return ZDRAW_CUDA_OK;
 }

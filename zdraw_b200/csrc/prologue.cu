@@ -13,8 +13,9 @@
 //   zflux2_glue_shader.zig:119-120).
 //
 // Mapping: 16 lanes per row, 8 consecutive elements per lane (one 16-byte load for
-// f16 input, two for f32; one 16-byte store). The sum of squares is reduced with
-// xor shuffles in a fixed order, so results are bit-identical run to run.
+// f16 input, two for f32; one 16-byte store); a 16-lane group walks several heads of one
+// token with that token's table and weight slices held in registers. The sum of squares is
+// reduced with xor shuffles in a fixed order, so results are bit-identical run to run.
 #include "prologue.cuh"
 
 #include <cuda_fp16.h>
@@ -25,7 +26,9 @@ namespace zdraw {
 
 namespace {
 
-constexpr int kRowsPerBlock = 16;  // 256 threads
+constexpr int kGroupsPerBlock = 16;  // 16-lane groups per 256-thread block
+constexpr int kHeadsPerGroup = 8;    // heads that share one load of the token's table and weight slices
+constexpr int kRowsInFlight = 4;     // rows loaded before the first is used
 constexpr float kHalfMax = 65504.0f;
 
 __device__ __forceinline__ void load8(const __half* p, float* x) {
@@ -52,34 +55,27 @@ __device__ __forceinline__ uint32_t pack_clamped(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// One 16-lane group owns (image, token, q-or-k, chunk of kHeadsPerGroup heads): it loads its
+// token's cos/sin slices and the weight slice once and reuses them for every head of the chunk,
+// so per 16 bytes of q/k the kernel issues one load and one store plus a small amortised share
+// of table loads. Rows are processed kRowsInFlight at a time to keep several loads in flight.
 template <typename TIn>
-__global__ void __launch_bounds__(kRowsPerBlock * 16)
-qk_norm_rope_kernel(const PrologueArgs a) {
-  const int which = blockIdx.y;  // 0 = q, 1 = k
-  const long long rows = static_cast<long long>(a.batch) * a.tokens * a.heads;
-  const long long row_raw = static_cast<long long>(blockIdx.x) * kRowsPerBlock + (threadIdx.x >> 4);
-  // Past the end: redo the last row and skip the store, so every lane reaches the shuffles.
-  const bool live = row_raw < rows;
-  const long long row = live ? row_raw : rows - 1;
+__global__ void __launch_bounds__(kGroupsPerBlock * 16, 3)
+qk_norm_rope_kernel(const PrologueArgs a, int n_chunks) {
+  const long long groups = static_cast<long long>(a.batch) * a.tokens * 2 * n_chunks;
+  const long long g_raw = static_cast<long long>(blockIdx.x) * kGroupsPerBlock + (threadIdx.x >> 4);
+  // Past the end: redo the last group and skip the stores, so every lane reaches the shuffles.
+  const bool live = g_raw < groups;
+  const long long g = live ? g_raw : groups - 1;
   const int sub = threadIdx.x & 15;
-  const int head = static_cast<int>(row % a.heads);
-  const long long bt = row / a.heads;
-  const int tok = static_cast<int>(bt % a.tokens);
-  const int img = static_cast<int>(bt / a.tokens);
-
-  const TIn* src = static_cast<const TIn*>(which ? a.k : a.q);
-  const long long ld = which ? a.ld_k : a.ld_q;
-  src += (static_cast<long long>(img) * a.tokens + tok) * ld + static_cast<long long>(head) * 128 + sub * 8;
-  float x[8];
-  load8(src, x);
-
-  float ss = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) ss = fmaf(x[i], x[i], ss);
-  // Lanes 0-15 and 16-31 of a warp hold different rows; offsets < 16 keep them apart.
-#pragma unroll
-  for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-  const float inv = 1.0f / sqrtf(ss * (1.0f / 128.0f) + a.eps);
+  const int tok = static_cast<int>(g % a.tokens);
+  long long rest = g / a.tokens;
+  const int chunk = static_cast<int>(rest % n_chunks);
+  rest /= n_chunks;
+  const int which = static_cast<int>(rest & 1);  // 0 = q, 1 = k
+  const int img = static_cast<int>(rest >> 1);
+  const int h_begin = chunk * kHeadsPerGroup;
+  const int h_end = min(h_begin + kHeadsPerGroup, a.heads);
 
   const float* w = (tok < a.txt_tokens) ? (which ? a.k_w_txt : a.q_w_txt) : (which ? a.k_w_img : a.q_w_img);
   float wv[8], cv[8], sv[8];
@@ -89,24 +85,49 @@ qk_norm_rope_kernel(const PrologueArgs a) {
   load8(a.rope_cos + rope_off, cv);
   load8(a.rope_sin + rope_off, sv);
 
-  uint32_t out[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float x0 = x[2 * i] * inv * wv[2 * i];
-    const float x1 = x[2 * i + 1] * inv * wv[2 * i + 1];
-    const float y0 = x0 * cv[2 * i] - x1 * sv[2 * i];
-    const float y1 = x1 * cv[2 * i + 1] + x0 * sv[2 * i + 1];
-    out[i] = pack_clamped(y0, y1);
+  const long long ld = which ? a.ld_k : a.ld_q;
+  const TIn* src = static_cast<const TIn*>(which ? a.k : a.q) +
+                   (static_cast<long long>(img) * a.tokens + tok) * ld + sub * 8;
+  __half* dst = static_cast<__half*>(which ? a.k_out : a.q_out);
+  long long dst_off, dst_head_stride;
+  if (a.out_head_major) {
+    dst_off = (static_cast<long long>(img) * a.heads * a.tokens + tok) * 128 + sub * 8;
+    dst_head_stride = static_cast<long long>(a.tokens) * 128;
+  } else {
+    dst_off = (static_cast<long long>(img) * a.tokens + tok) * a.heads * 128 + sub * 8;
+    dst_head_stride = 128;
   }
 
-  __half* dst = static_cast<__half*>(which ? a.k_out : a.q_out);
-  long long off;
-  if (a.out_head_major) {
-    off = ((static_cast<long long>(img) * a.heads + head) * a.tokens + tok) * 128;
-  } else {
-    off = ((static_cast<long long>(img) * a.tokens + tok) * a.heads + head) * 128;
+  for (int h0 = h_begin; h0 < h_end; h0 += kRowsInFlight) {
+    float x[kRowsInFlight][8];
+#pragma unroll
+    for (int r = 0; r < kRowsInFlight; ++r) {
+      const int h = min(h0 + r, h_end - 1);  // clamp: a repeated row is computed and not stored
+      load8(src + static_cast<long long>(h) * 128, x[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < kRowsInFlight; ++r) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss = fmaf(x[r][i], x[r][i], ss);
+      // Lanes 0-15 and 16-31 of a warp hold different groups; offsets < 16 keep them apart.
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+      const float inv = 1.0f / sqrtf(ss * (1.0f / 128.0f) + a.eps);
+      uint32_t out[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float x0 = x[r][2 * i] * inv * wv[2 * i];
+        const float x1 = x[r][2 * i + 1] * inv * wv[2 * i + 1];
+        const float y0 = x0 * cv[2 * i] - x1 * sv[2 * i];
+        const float y1 = x1 * cv[2 * i + 1] + x0 * sv[2 * i + 1];
+        out[i] = pack_clamped(y0, y1);
+      }
+      const int h = h0 + r;
+      if (live && h < h_end)
+        *reinterpret_cast<uint4*>(dst + dst_off + h * dst_head_stride) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
   }
-  if (live) *reinterpret_cast<uint4*>(dst + off + sub * 8) = make_uint4(out[0], out[1], out[2], out[3]);
 }
 
 // f32 token-major (ld) -> f16 token-major dense; the cast the reference does in
@@ -130,12 +151,13 @@ __global__ void cast_f32_to_f16_kernel(const float* src, __half* dst, long long 
 }  // namespace
 
 cudaError_t launch_qk_norm_rope(cudaStream_t stream, const PrologueArgs& a, bool in_f32) {
-  const long long rows = static_cast<long long>(a.batch) * a.tokens * a.heads;
-  const dim3 grid(static_cast<unsigned>((rows + kRowsPerBlock - 1) / kRowsPerBlock), 2);
+  const int n_chunks = (a.heads + kHeadsPerGroup - 1) / kHeadsPerGroup;
+  const long long groups = static_cast<long long>(a.batch) * a.tokens * 2 * n_chunks;
+  const unsigned grid = static_cast<unsigned>((groups + kGroupsPerBlock - 1) / kGroupsPerBlock);
   if (in_f32) {
-    qk_norm_rope_kernel<float><<<grid, kRowsPerBlock * 16, 0, stream>>>(a);
+    qk_norm_rope_kernel<float><<<grid, kGroupsPerBlock * 16, 0, stream>>>(a, n_chunks);
   } else {
-    qk_norm_rope_kernel<__half><<<grid, kRowsPerBlock * 16, 0, stream>>>(a);
+    qk_norm_rope_kernel<__half><<<grid, kGroupsPerBlock * 16, 0, stream>>>(a, n_chunks);
   }
   return cudaGetLastError();
 }
