@@ -155,7 +155,7 @@ def run_reference(args, rank: int):
 
     w = workloads.WORKLOADS[args.workload]
     oracle.build()
-    cores = oracle.num_threads()
+    cores = oracle.use_all_cores()
     timer = OracleTimer(w)
     # Size a step to about 2 s of CPU work, bounded so that the whole run stays within minutes.
     budget = min(2.0, 120.0 / max(args.steps + args.warmup, 1))
@@ -193,6 +193,10 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU-baseline sample budget")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = min(steps, 20)")
+    ap.add_argument("--shard", default="images", choices=["images", "heads"],
+                    help="images: one image per rank (weak scaling); heads: one call's heads split over ranks (strong)")
+    ap.add_argument("--allgather", action="store_true",
+                    help="with --shard heads: NCCL all-gather of the head-major outputs inside the step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -221,12 +225,23 @@ def main():
         torch.cuda.synchronize()
 
     w0 = workloads.WORKLOADS[args.workload]
-    # Each rank works on its own image(s): a different seed per rank.
     from dataclasses import replace
 
-    w = replace(w0, seed=w0.seed + 1000 * rank)
+    from zdraw_b200 import shard as shardlib
+
+    by_heads = args.shard == "heads" and world > 1
+    if by_heads:
+        # Same call on every rank (same seed); this rank computes heads [h0, h1) of it.
+        w = w0
+        hs = shardlib.split(w.heads, world, rank)
+    else:
+        # Each rank works on its own image(s): a different seed per rank.
+        w = replace(w0, seed=w0.seed + 1000 * rank)
+        hs = shardlib.Shard(rank, world, 0, w.heads)
     ctx = mattn.Context(local_rank)
-    p = workloads.params(w)
+    ld = w.heads * 128
+    p = workloads.params(w, heads=hs.count, ld_q=ld, ld_k=ld, ld_v=ld, ld_o=ld,
+                         out_layout=1 if by_heads else 0)
     ctx.reserve(p)
 
     # Buffer sets: enough copies that one pass over all of them exceeds L2.
@@ -235,13 +250,19 @@ def main():
     n_sets = max(2, int(3 * L2_BYTES // step_bytes) + 1)
     sets = [x0] + [{k: (v.clone() if (v is not None and k in ("q", "k", "v")) else v) for k, v in x0.items()}
                    for _ in range(n_sets - 1)]
-    outs = [torch.empty((w.batch, w.tokens, w.heads, 128), dtype=x0["q"].dtype, device="cuda") for _ in range(n_sets)]
+    out_shape = (w.batch, hs.count, w.tokens, 128) if by_heads else (w.batch, w.tokens, w.heads, 128)
+    outs = [torch.empty(out_shape, dtype=x0["q"].dtype, device="cuda") for _ in range(n_sets)]
     stream = torch.cuda.current_stream()
+    hsl = slice(hs.begin, hs.end)
 
     def step(i):
         x = sets[i % n_sets]
-        ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
-                            x["rope_cos"], x["rope_sin"], outs[i % n_sets], p, key_mask=x["key_mask"], stream=stream)
+        # A head shard is a column slice: same token stride, pointer offset h0 * 128.
+        ctx.joint_attention(x["q"][:, :, hsl], x["k"][:, :, hsl], x["v"][:, :, hsl], x["q_w_txt"], x["q_w_img"],
+                            x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"], outs[i % n_sets], p,
+                            key_mask=x["key_mask"], stream=stream)
+        if by_heads and args.allgather:
+            shardlib.all_gather_heads(outs[i % n_sets][0], w.heads, rank, world)
 
     launches_per_step = 2 + (1 if w.masked_text is not None else 0) + (1 if w.dtype == "f32" else 0)
 
@@ -263,18 +284,18 @@ def main():
         raise SystemExit("a kernel reported a non-zero status during the timed region")
 
     # ---- attention kernel alone (dominant kernel) and prologue alone
-    q16 = [torch.empty((w.batch, w.heads, w.tokens, 128), dtype=torch.float16, device="cuda") for _ in range(n_sets)]
+    q16 = [torch.empty((w.batch, hs.count, w.tokens, 128), dtype=torch.float16, device="cuda") for _ in range(n_sets)]
     k16 = [torch.empty_like(q16[0]) for _ in range(n_sets)]
 
     def prologue(i):
         x = sets[i % n_sets]
-        ctx.qk_norm_rope(x["q"], x["k"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"], x["rope_cos"],
-                         x["rope_sin"], q16[i % n_sets], k16[i % n_sets], p, stream=stream)
+        ctx.qk_norm_rope(x["q"][:, :, hsl], x["k"][:, :, hsl], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                         x["rope_cos"], x["rope_sin"], q16[i % n_sets], k16[i % n_sets], p, stream=stream)
 
     def attention(i):
         x = sets[i % n_sets]
-        ctx.run_on_handles(q16[i % n_sets], k16[i % n_sets], x["v"], outs[i % n_sets], p, key_mask=x["key_mask"],
-                           stream=stream)
+        ctx.run_on_handles(q16[i % n_sets], k16[i % n_sets], x["v"][:, :, hsl], outs[i % n_sets], p,
+                           key_mask=x["key_mask"], stream=stream)
 
     def timed(fn):
         for i in range(max(3, args.warmup)):
@@ -293,14 +314,18 @@ def main():
 
     # ---- end to end from pinned host buffers through the host-buffer C-ABI entry point
     xh = workloads.make_inputs(w, "cpu", pin=True)
-    oh = torch.empty((w.batch, w.tokens, w.heads, 128), dtype=xh["q"].dtype).pin_memory()
+    p_host = workloads.params(w, heads=hs.count, out_layout=1 if by_heads else 0)
+    if by_heads:
+        for n in ("q", "k", "v"):
+            xh[n] = xh[n][:, :, hsl].contiguous().pin_memory()
+    oh = torch.empty(out_shape, dtype=xh["q"].dtype).pin_memory()
     h2d = sum(xh[n].numel() * xh[n].element_size() for n in xh if xh[n] is not None)
     d2h = oh.numel() * oh.element_size()
     e2e_steps = args.e2e_steps or min(args.steps, 20)
 
     def e2e_step():
         ctx.joint_attention_host(xh["q"], xh["k"], xh["v"], xh["q_w_txt"], xh["q_w_img"], xh["k_w_txt"],
-                                 xh["k_w_img"], xh["rope_cos"], xh["rope_sin"], oh, p, key_mask=xh["key_mask"])
+                                 xh["k_w_img"], xh["rope_cos"], xh["rope_sin"], oh, p_host, key_mask=xh["key_mask"])
 
     for _ in range(3):
         e2e_step()
@@ -318,13 +343,14 @@ def main():
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms_total, ms_prologue, ms_attention, ms_e2e = times.tolist()
 
-    flops_rank = w.flops
+    flops_rank = w.flops * hs.count / w.heads
     ms_step = ms_total / args.steps
-    value = world * flops_rank / (ms_step * 1e-3) / 1e12
+    total_flops = w.flops if by_heads else world * w.flops
+    value = total_flops / (ms_step * 1e-3) / 1e12
     attn_tflops = flops_rank / (ms_attention * 1e-3) / 1e12
-    e2e_value = world * flops_rank / (ms_e2e * 1e-3) / 1e12
+    e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
     in_size = 4 if w.dtype == "f32" else 2
-    elems = w.batch * w.tokens * w.heads * 128
+    elems = w.batch * w.tokens * hs.count * 128
     prologue_bytes = 2 * elems * in_size + 2 * elems * 2 + 2 * w.tokens * 128 * 4
     prologue_gbs = prologue_bytes / (ms_prologue * 1e-3) / 1e9
 
@@ -333,11 +359,13 @@ def main():
         line = {
             "metric": "attention TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)", "data": "synthetic",
+            "scaling": "strong" if by_heads else "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)",
+            "data": "synthetic",
             "config": {
                 "workload": w.name, "batch_per_gpu": w.batch, "heads": w.heads, "tokens": w.tokens, "head_dim": 128,
                 "flops_per_step_per_gpu": flops_rank, "step": "qk_norm_rope prologue + attention (joint call)",
-                "sharding": "one image (seed) per GPU, no collective",
+                "sharding": ("heads split over GPUs" + (", NCCL all-gather of O inside the step" if args.allgather
+                             else ", no collective")) if by_heads else "one image (seed) per GPU, no collective",
                 "l2": f"inputs rotate over {n_sets} buffer sets ({n_sets * step_bytes / 1e6:.0f} MB > 126 MB L2)",
             },
             "roofline": {
@@ -361,6 +389,7 @@ def main():
             import oracle
 
             oracle.build()
+            oracle.use_all_cores()
             timer = OracleTimer(w)
             rows = timer.rows_for(args.cpu_seconds)
             dt = timer.run(rows)

@@ -69,6 +69,8 @@ def lib() -> C.CDLL:
         _lib.orc_joint_attention.argtypes = [fp] * 13 + [sz, sz, sz, sz, C.c_int, C.c_float, sz, sz]
         _lib.orc_joint_attention.restype = C.c_int
         _lib.orc_num_threads.restype = C.c_int
+        _lib.orc_set_num_threads.argtypes = [C.c_int]
+        _lib.orc_set_num_threads.restype = None
     return _lib
 
 
@@ -88,6 +90,13 @@ def _sz3(v) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def use_all_cores() -> int:
+    """Use every core this process may run on, whatever OMP_NUM_THREADS says; returns the count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(n)
+    return num_threads()
 
 
 def sdpa(q, k, v, heads: int, kv_heads: int | None = None, causal: bool = False, valid: int = 0,

@@ -448,6 +448,15 @@ ORC_API int orc_joint_attention(float *out, float *qn, float *kn, const float *q
                        tok_begin, tok_end);
 }
 
+/* Overrides OMP_NUM_THREADS (launchers such as torchrun export OMP_NUM_THREADS=1). */
+ORC_API void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -205,6 +205,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = flags[1];
 
+  // Everything above overlaps the tail of the preceding kernel (the prologue) when the launch
+  // allows it; from here on this kernel reads what earlier kernels wrote.
+  grid_dependency_wait();
+
   // Coordinates of (token row, head) in the two tensor-map dimension orders.
   auto c1 = [&](int hm, int tok) { return hm ? tok : head; };
   auto c2 = [&](int hm, int tok) { return hm ? head : tok; };
@@ -650,12 +654,20 @@ cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const 
                             const CUtensorMap& tm_v, const AttnArgs& args) {
   const int n_q_tiles = (args.tokens + kBM - 1) / kBM;
   dim3 grid((n_q_tiles + 1) / 2, args.heads, args.batch);
-  if (args.trace != nullptr) {
-    attn_fwd_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, args);
-  } else {
-    attn_fwd_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, args);
-  }
-  return cudaGetLastError();
+  // Programmatic dependent launch: the kernel may become resident while the preceding kernel in
+  // the stream drains; it calls griddepcontrol.wait before touching that kernel's results.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (args.trace != nullptr) return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<true>, tm_q, tm_k, tm_v, args);
+  return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<false>, tm_q, tm_k, tm_v, args);
 }
 
 cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args) {

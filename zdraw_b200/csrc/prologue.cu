@@ -18,6 +18,8 @@
 // reduced with xor shuffles in a fixed order, so results are bit-identical run to run.
 #include "prologue.cuh"
 
+#include "ptx.cuh"
+
 #include <cuda_fp16.h>
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -62,6 +64,9 @@ __device__ __forceinline__ uint32_t pack_clamped(float lo, float hi) {
 template <typename TIn>
 __global__ void __launch_bounds__(kGroupsPerBlock * 16, 3)
 qk_norm_rope_kernel(const PrologueArgs a, int n_chunks) {
+  // The attention kernel that follows may start its preamble (barriers, TMEM) now; it waits for
+  // this grid to finish before it reads q/k.
+  grid_launch_dependents();
   const long long groups = static_cast<long long>(a.batch) * a.tokens * 2 * n_chunks;
   const long long g_raw = static_cast<long long>(blockIdx.x) * kGroupsPerBlock + (threadIdx.x >> 4);
   // Past the end: redo the last group and skip the stores, so every lane reaches the shuffles.

@@ -16,6 +16,17 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// In a kernel launched with the programmatic-stream-serialization attribute: returns once the
+// preceding kernel in the stream has completed and its writes are visible. A no-op otherwise.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets a dependent kernel launched with that attribute start its preamble while this grid runs.
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
