@@ -197,3 +197,30 @@ def test_joint_tiny_config_f32(ctx, oracle):
     ctx.joint_attention_host(h["q"], h["k"], h["v"], h["q_w_txt"], h["q_w_img"], h["k_w_txt"], h["k_w_img"],
                              h["rope_cos"], h["rope_sin"], out_h, p)
     assert np.array_equal(out_h, out.cpu().numpy())
+
+
+def test_pipeline_trace_facility(ctx):
+    """zdraw_cuda_attn_set_trace: the instrumented kernel gives the same bytes and monotonic stamps."""
+    import ctypes as C
+
+    w = workloads.Workload("trace_case", "klein", 1, 2, 512, 16, 16, seed=5)  # S = 768: 6 K/V steps
+    x = workloads.make_inputs(w, "cuda")
+    p = workloads.params(w)
+    plain = torch.empty((1, w.tokens, w.heads, 128), dtype=torch.float16, device="cuda")
+    traced = torch.empty_like(plain)
+    args = (x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"])
+    ctx.joint_attention(*args, plain, p)
+    words = torch.zeros(960, dtype=torch.int64, device="cuda")
+    lib = _lib.lib()
+    assert lib.zdraw_cuda_attn_set_trace(ctx._h, C.c_void_p(words.data_ptr()), 100) == _lib.E_ARG  # too small
+    assert lib.zdraw_cuda_attn_set_trace(ctx._h, C.c_void_p(words.data_ptr()), 960) == 0
+    try:
+        ctx.joint_attention(*args, traced, p)
+        torch.cuda.synchronize()
+    finally:
+        assert lib.zdraw_cuda_attn_set_trace(ctx._h, None, 0) == 0
+    assert torch.equal(plain.view(torch.int16), traced.view(torch.int16))
+    t = words.cpu().numpy().reshape(3, 40, 8)
+    mma_steps = t[0, :6, 0]
+    assert (mma_steps > 0).all() and (np.diff(mma_steps) > 0).all(), "MMA step stamps must increase"
+    assert not t[0, 6:].any(), "only six K/V steps were run"
