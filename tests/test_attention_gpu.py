@@ -210,17 +210,17 @@ def test_pipeline_trace_facility(ctx):
     traced = torch.empty_like(plain)
     args = (x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"])
     ctx.joint_attention(*args, plain, p)
-    words = torch.zeros(960, dtype=torch.int64, device="cuda")
+    words = torch.zeros(1600, dtype=torch.int64, device="cuda")
     lib = _lib.lib()
     assert lib.zdraw_cuda_attn_set_trace(ctx._h, C.c_void_p(words.data_ptr()), 100) == _lib.E_ARG  # too small
-    assert lib.zdraw_cuda_attn_set_trace(ctx._h, C.c_void_p(words.data_ptr()), 960) == 0
+    assert lib.zdraw_cuda_attn_set_trace(ctx._h, C.c_void_p(words.data_ptr()), 1600) == 0
     try:
         ctx.joint_attention(*args, traced, p)
         torch.cuda.synchronize()
     finally:
         assert lib.zdraw_cuda_attn_set_trace(ctx._h, None, 0) == 0
     assert torch.equal(plain.view(torch.int16), traced.view(torch.int16))
-    t = words.cpu().numpy().reshape(3, 40, 8)
+    t = words.cpu().numpy().reshape(5, 40, 8)  # [role][K/V step][event]
     mma_steps = t[0, :6, 0]
     assert (mma_steps > 0).all() and (np.diff(mma_steps) > 0).all(), "MMA step stamps must increase"
     assert not t[0, 6:].any(), "only six K/V steps were run"

@@ -50,10 +50,11 @@ __device__ __forceinline__ void load8(const float* p, float* x) {
   x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
 }
 
+// Rounds to f16 and clamps to +-65504 (an overflow rounds to +-inf first, then clamps).
 __device__ __forceinline__ uint32_t pack_clamped(float lo, float hi) {
-  lo = fminf(fmaxf(lo, -kHalfMax), kHalfMax);
-  hi = fminf(fmaxf(hi, -kHalfMax), kHalfMax);
-  const __half2 h = __floats2half2_rn(lo, hi);
+  const __half2 lim = __float2half2_rn(kHalfMax);
+  __half2 h = __floats2half2_rn(lo, hi);
+  h = __hmin2(__hmax2(h, __hneg2(lim)), lim);
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
@@ -89,6 +90,16 @@ qk_norm_rope_kernel(const PrologueArgs a, int n_chunks) {
                              static_cast<long long>(tok) * 128 + sub * 8;
   load8(a.rope_cos + rope_off, cv);
   load8(a.rope_sin + rope_off, sv);
+  // y0 = (x0 inv w0) c0 - (x1 inv w1) s0 = inv (x0 (w0 c0) - x1 (w1 s0)), likewise y1: the weight
+  // is folded into the rotation coefficients once per token, not once per head.
+  float ca[8], sb[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    ca[2 * i] = wv[2 * i] * cv[2 * i];              // x0 coefficient of y0
+    sb[2 * i] = wv[2 * i + 1] * sv[2 * i];          // x1 coefficient of y0
+    ca[2 * i + 1] = wv[2 * i + 1] * cv[2 * i + 1];  // x1 coefficient of y1
+    sb[2 * i + 1] = wv[2 * i] * sv[2 * i + 1];      // x0 coefficient of y1
+  }
 
   const long long ld = which ? a.ld_k : a.ld_q;
   const TIn* src = static_cast<const TIn*>(which ? a.k : a.q) +
@@ -122,10 +133,9 @@ qk_norm_rope_kernel(const PrologueArgs a, int n_chunks) {
       uint32_t out[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const float x0 = x[r][2 * i] * inv * wv[2 * i];
-        const float x1 = x[r][2 * i + 1] * inv * wv[2 * i + 1];
-        const float y0 = x0 * cv[2 * i] - x1 * sv[2 * i];
-        const float y1 = x1 * cv[2 * i + 1] + x0 * sv[2 * i + 1];
+        const float x0 = x[r][2 * i], x1 = x[r][2 * i + 1];
+        const float y0 = (x0 * ca[2 * i] - x1 * sb[2 * i]) * inv;
+        const float y1 = (x1 * ca[2 * i + 1] + x0 * sb[2 * i + 1]) * inv;
         out[i] = pack_clamped(y0, y1);
       }
       const int h = h0 + r;
