@@ -239,6 +239,43 @@ ZDRAW_CUDA_API int zdraw_cuda_zimage_rope_table(float *cos_out, float *sin_out, 
 ZDRAW_CUDA_API int zdraw_cuda_last_status(void *ctx, void *stream, uint32_t *device_status);
 
 /*
+ * Projection GEMM for the steps either side of attention: C[m, n] = A[m, k] * W[n, k]^T with f16
+ * A and W and f32 accumulation. Replaces zdraw_metal_run_gemm_enc as the DiT blocks use it for
+ * the q/k/v and output projections (gemmRunF16A, src/klein/zflux2_resident.zig:924-990; call
+ * sites :1473-1513, 1986-1998, 2038-2039; CPU meaning src/runtime/ops.zig:18-36).
+ *   epilogue 0: C stored as c_dtype, row-major with stride ld_c.
+ *   epilogue 1: the attention prologue is applied to the accumulator instead (per-head RMSNorm
+ *               with norm_w_txt / norm_w_img, RoPE from the per-token tables, clamp, fp16) and C
+ *               is the head-major [image][head][token][128] buffer zdraw_cuda_attention takes
+ *               with qk_layout = ZDRAW_LAYOUT_HEAD_MAJOR: the q/k projection and krms_rope_hm in
+ *               one pass, without the reference's f32 q/k round trip through memory.
+ * n must be a multiple of 256 and k of 64, else the call is declined.
+ */
+typedef struct zdraw_cuda_linear_params {
+  uint32_t m, n, k;
+  uint32_t a_dtype, w_dtype, c_dtype; /* ZDRAW_DTYPE_*; A and W must be f16 */
+  uint32_t epilogue;                  /* 0 plain, 1 qk-norm-rope */
+  uint32_t reserved;                  /* must be 0 */
+  uint64_t ld_a, ld_w, ld_c;          /* row strides in elements; 0 => k, k, n */
+  /* epilogue 1: m = images * tokens, n = heads * 128 */
+  uint32_t tokens, heads, txt_tokens;
+  float norm_eps;
+  uint64_t rope_batch_stride;
+} zdraw_cuda_linear_params;
+
+#define ZDRAW_CUDA_LINEAR_PARAMS_SIZE 80
+#if defined(__cplusplus)
+static_assert(sizeof(zdraw_cuda_linear_params) == ZDRAW_CUDA_LINEAR_PARAMS_SIZE, "ABI size");
+#else
+_Static_assert(sizeof(zdraw_cuda_linear_params) == ZDRAW_CUDA_LINEAR_PARAMS_SIZE, "ABI size");
+#endif
+
+ZDRAW_CUDA_API int zdraw_cuda_linear(void *ctx, void *stream, const void *a, const void *w, void *c,
+                                     const float *norm_w_txt, const float *norm_w_img,
+                                     const float *rope_cos, const float *rope_sin,
+                                     const zdraw_cuda_linear_params *p);
+
+/*
  * Debugging aid, the counterpart of ZDRAW_KLEIN_TRACE's per-stage GPU times
  * (src/klein/zflux2_resident.zig:380-409): while a device buffer of at least 1600 64-bit words is
  * set, the first CTA of every attention launch writes clock stamps of its pipeline events

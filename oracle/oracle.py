@@ -68,6 +68,8 @@ def lib() -> C.CDLL:
         _lib.orc_qk_prologue.restype = None
         _lib.orc_joint_attention.argtypes = [fp] * 13 + [sz, sz, sz, sz, C.c_int, C.c_float, sz, sz]
         _lib.orc_joint_attention.restype = C.c_int
+        _lib.orc_linear_rows.argtypes = [fp, fp, fp, sz, sz, sz, sz, sz]
+        _lib.orc_linear_rows.restype = None
         _lib.orc_num_threads.restype = C.c_int
         _lib.orc_set_num_threads.argtypes = [C.c_int]
         _lib.orc_set_num_threads.restype = None
@@ -278,3 +280,19 @@ def joint_attention(q, k, v, qw_txt, qw_img, kw_txt, kw_img, cos_t, sin_t, heads
     if return_qk:
         return out, qn, kn
     return out
+
+
+def linear(a, w, rows: tuple[int, int] | None = None) -> np.ndarray:
+    """``linear`` (src/runtime/ops.zig:18-36) on every row: c = a @ w.T with sequential f32 sums.
+
+    a [m, k], w [n, k]; with ``rows`` only those rows of c are filled.
+    """
+    a = _f32(a)
+    w = _f32(w)
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k
+    c = np.zeros((m, n), np.float32)
+    b, e = (0, m) if rows is None else rows
+    lib().orc_linear_rows(_p(c), _p(a), _p(w), m, n, k, b, e)
+    return c

@@ -448,6 +448,25 @@ ORC_API int orc_joint_attention(float *out, float *qn, float *kn, const float *q
                        tok_begin, tok_end);
 }
 
+/* ------------------------------------------------------------------------- */
+/* Projection either side of attention: src/runtime/ops.zig:18-36            */
+/* ------------------------------------------------------------------------- */
+
+/*
+ * linear (ops.zig:18-36) applied to every row of a: c[r][j] = dot(a[r], w[j]) with the
+ * sequential f32 sum of ops.zig:11-16; w is [n][k] row-major, no bias (the DiT projections
+ * have none). Rows [row_begin, row_end) of c are filled.
+ */
+ORC_API void orc_linear_rows(float *c, const float *a, const float *w, size_t m, size_t n, size_t k,
+                             size_t row_begin, size_t row_end) {
+  (void)m;
+#pragma omp parallel for schedule(static)
+  for (ptrdiff_t r = (ptrdiff_t)row_begin; r < (ptrdiff_t)row_end; ++r) {
+    const float *ar = a + (size_t)r * k;
+    for (size_t j = 0; j < n; ++j) c[(size_t)r * n + j] = orc_dot(ar, w + j * k, k);
+  }
+}
+
 /* Overrides OMP_NUM_THREADS (launchers such as torchrun export OMP_NUM_THREADS=1). */
 ORC_API void orc_set_num_threads(int n) {
 #ifdef _OPENMP

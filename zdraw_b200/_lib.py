@@ -48,6 +48,20 @@ class AttnParams(C.Structure):
     ]
 
 
+class LinearParams(C.Structure):
+    """``zdraw_cuda_linear_params`` (include/zdraw_cuda.h); 80 bytes."""
+
+    _fields_ = [
+        ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32),
+        ("a_dtype", C.c_uint32), ("w_dtype", C.c_uint32), ("c_dtype", C.c_uint32),
+        ("epilogue", C.c_uint32), ("reserved", C.c_uint32),
+        ("ld_a", C.c_uint64), ("ld_w", C.c_uint64), ("ld_c", C.c_uint64),
+        ("tokens", C.c_uint32), ("heads", C.c_uint32), ("txt_tokens", C.c_uint32),
+        ("norm_eps", C.c_float),
+        ("rope_batch_stride", C.c_uint64),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/zdraw_cuda.h declares.
 _VP, _PP = C.c_void_p, C.POINTER(AttnParams)
 SYMBOLS = {
@@ -64,6 +78,7 @@ SYMBOLS = {
     "zdraw_cuda_klein_rope_table": (C.c_int, [_VP, _VP] + [C.c_size_t] * 5 + [C.c_double]),
     "zdraw_cuda_zimage_rope_table": (C.c_int, [_VP, _VP] + [C.c_size_t] * 3 + [_VP, _VP, C.c_float]),
     "zdraw_cuda_last_status": (C.c_int, [_VP, _VP, C.POINTER(C.c_uint32)]),
+    "zdraw_cuda_linear": (C.c_int, [_VP] * 9 + [C.POINTER(LinearParams)]),
     "zdraw_cuda_attn_set_trace": (C.c_int, [_VP, _VP, C.c_size_t]),
     "zdraw_cuda_last_error": (C.c_char_p, [_VP]),
 }
@@ -93,6 +108,8 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.restype = restype
             fn.argtypes = argtypes
+        if C.sizeof(LinearParams) != 80:
+            raise RuntimeError("ABI mismatch: zdraw_cuda_linear_params is 80 bytes")
         if handle.zdraw_cuda_attn_params_size() != C.sizeof(AttnParams):
             raise RuntimeError("ABI mismatch: sizeof(zdraw_cuda_attn_params) differs between library and binding")
         _lib = handle

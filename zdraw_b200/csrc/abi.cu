@@ -13,6 +13,7 @@
 
 #include "../../include/zdraw_cuda.h"
 #include "attention_fwd.cuh"
+#include "linear.cuh"
 #include "prologue.cuh"
 
 namespace {
@@ -40,6 +41,7 @@ struct Ctx {
   int device = 0;
   uint32_t* d_status = nullptr;
   EncodeTiledFn encode = nullptr;
+  int sm_count = 0;
   cudaStream_t host_stream = nullptr;  // used by the host-buffer entry point only
   unsigned long long* d_trace = nullptr;  // caller's trace buffer while pipeline tracing is on (debugging)
   // Grow-only scratch (device memory).
@@ -346,6 +348,7 @@ int zdraw_cuda_attn_create(int device, void** ctx_out) {
   Ctx* c = new (std::nothrow) Ctx();
   if (!c) return ZDRAW_CUDA_E_CUDA;
   c->device = device;
+  c->sm_count = prop.multiProcessorCount;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn ||
@@ -357,7 +360,7 @@ int zdraw_cuda_attn_create(int device, void** ctx_out) {
   if (cudaMalloc(reinterpret_cast<void**>(&c->d_status), 256) != cudaSuccess ||
       cudaMemset(c->d_status, 0, 256) != cudaSuccess ||
       cudaStreamCreateWithFlags(&c->host_stream, cudaStreamNonBlocking) != cudaSuccess ||
-      zdraw::attn_fwd_configure() != cudaSuccess) {
+      zdraw::attn_fwd_configure() != cudaSuccess || zdraw::linear_configure() != cudaSuccess) {
     if (c->d_status) cudaFree(c->d_status);
     if (c->host_stream) cudaStreamDestroy(c->host_stream);
     delete c;
@@ -539,6 +542,72 @@ int zdraw_cuda_last_status(void* ctx, void* stream, uint32_t* device_status) {
   ZD_CUDA(c, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   ZD_CUDA(c, cudaMemcpy(device_status, c->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
   if (*device_status != 0) ZD_CUDA(c, cudaMemset(c->d_status, 0, sizeof(uint32_t)));
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_linear(void* ctx, void* stream, const void* a, const void* w, void* c, const float* norm_w_txt,
+                      const float* norm_w_img, const float* rope_cos, const float* rope_sin,
+                      const zdraw_cuda_linear_params* p) {
+  Ctx* cx = as_ctx(ctx);
+  if (!cx) return ZDRAW_CUDA_E_ARG;
+  if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
+  if (p->reserved != 0 || p->m == 0 || p->n == 0 || p->k == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero size or reserved != 0");
+  if (p->epilogue > 1 || (p->c_dtype != ZDRAW_DTYPE_F16 && p->c_dtype != ZDRAW_DTYPE_F32))
+    return fail(cx, ZDRAW_CUDA_E_ARG, "bad epilogue or c_dtype");
+  if (!a || !w || !c || !aligned16(a) || !aligned16(w) || !aligned16(c)) return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned matrix");
+  // Shapes and types outside the kernel: declined, nothing enqueued (the reference's fast GEMMs
+  // admit 32-aligned dims only, src/metal/mres_util.zig:30-38).
+  if (p->a_dtype != ZDRAW_DTYPE_F16 || p->w_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_DECLINED, "A and W must be f16");
+  if (p->n % 256 != 0 || p->k % 64 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "n must be a multiple of 256 and k of 64");
+  if (p->m > (1u << 30) || p->n > (1u << 30) || p->k > (1u << 30)) return fail(cx, ZDRAW_CUDA_DECLINED, "shape too large");
+  const long long ld_a = p->ld_a ? static_cast<long long>(p->ld_a) : p->k;
+  const long long ld_w = p->ld_w ? static_cast<long long>(p->ld_w) : p->k;
+  const long long ld_c = p->ld_c ? static_cast<long long>(p->ld_c) : p->n;
+  if (ld_a < p->k || ld_w < p->k || ld_c < p->n) return fail(cx, ZDRAW_CUDA_E_ARG, "row stride smaller than the row");
+  if (ld_a % 8 != 0 || ld_w % 8 != 0 || ld_c % 8 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "row strides must be multiples of 8");
+  zdraw::LinearArgs la = {};
+  la.m = static_cast<int>(p->m);
+  la.n = static_cast<int>(p->n);
+  la.k = static_cast<int>(p->k);
+  la.epilogue = static_cast<int>(p->epilogue);
+  la.c_f32 = p->c_dtype == ZDRAW_DTYPE_F32;
+  la.c = c;
+  la.ld_c = ld_c;
+  la.status = cx->d_status;
+  if (p->epilogue == 1) {
+    if (p->tokens == 0 || p->heads == 0 || p->m % p->tokens != 0 || p->n != p->heads * 128u || p->txt_tokens > p->tokens)
+      return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs m = images * tokens and n = heads * 128");
+    if (p->c_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_E_ARG, "the qk epilogue writes f16");
+    if (!norm_w_txt || !norm_w_img || !rope_cos || !rope_sin || !aligned16(norm_w_txt) || !aligned16(norm_w_img) ||
+        !aligned16(rope_cos) || !aligned16(rope_sin) || p->rope_batch_stride % 4 != 0)
+      return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs aligned weights and tables");
+    if (!(p->norm_eps >= 0.0f)) return fail(cx, ZDRAW_CUDA_E_ARG, "norm_eps must be >= 0");
+    la.tokens = static_cast<int>(p->tokens);
+    la.heads = static_cast<int>(p->heads);
+    la.txt_tokens = static_cast<int>(p->txt_tokens);
+    la.norm_eps = p->norm_eps;
+    la.w_txt = norm_w_txt;
+    la.w_img = norm_w_img;
+    la.rope_cos = rope_cos;
+    la.rope_sin = rope_sin;
+    la.rope_batch_stride = static_cast<long long>(p->rope_batch_stride);
+  }
+  ZD_CUDA(cx, cudaSetDevice(cx->device));
+  // Row-major f16 matrices [rows][ld] as tiled tensor maps: boxes of 64 columns x 128 (A) or 256 (W) rows.
+  CUtensorMap tm_a, tm_w;
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  auto encode = [&](CUtensorMap* tm, const void* base_ptr, uint64_t rows, long long ld, uint32_t box_rows) {
+    const cuuint64_t dims[4] = {p->k, rows, 1, 1};
+    const cuuint64_t strides[3] = {2ull * static_cast<cuuint64_t>(ld), 2ull * static_cast<cuuint64_t>(ld) * rows,
+                                   2ull * static_cast<cuuint64_t>(ld) * rows};
+    const cuuint32_t box[4] = {64, box_rows, 1, 1};
+    return cx->encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base_ptr), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  if (encode(&tm_a, a, p->m, ld_a, 128) != CUDA_SUCCESS || encode(&tm_w, w, p->n, ld_w, 256) != CUDA_SUCCESS)
+    return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
+  ZD_CUDA(cx, zdraw::launch_linear(static_cast<cudaStream_t>(stream), tm_a, tm_w, la, cx->sm_count));
   return ZDRAW_CUDA_OK;
 }
 

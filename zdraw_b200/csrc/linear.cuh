@@ -1,0 +1,34 @@
+// Launch interface of the projection GEMM (internal to the library).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace zdraw {
+
+constexpr int kEpiloguePlain = 0;
+constexpr int kEpilogueQk = 1;
+
+// C[m, n] = A[m, k] * W[n, k]^T. A and W are reached through tensor maps (f16, 128-byte swizzle,
+// boxes 64 x 128 and 64 x 256). n % 256 == 0, k % 64 == 0.
+struct LinearArgs {
+  int m, n, k;
+  int epilogue;  // kEpiloguePlain | kEpilogueQk
+  int c_f32;     // plain: 1 = f32 C, 0 = f16 C
+  void* c;       // plain: [m][ld_c]; qk: f16 head-major [image][head][token][128]
+  long long ld_c;
+  // qk epilogue (n == heads * 128, m == images * tokens)
+  int tokens, heads, txt_tokens;
+  float norm_eps;
+  const float *w_txt, *w_img;        // [128]
+  const float *rope_cos, *rope_sin;  // [tokens][128]
+  long long rope_batch_stride;
+  uint32_t* status;
+};
+
+cudaError_t linear_configure();
+cudaError_t launch_linear(cudaStream_t stream, const CUtensorMap& tm_a, const CUtensorMap& tm_w,
+                          const LinearArgs& args, int sm_count);
+
+}  // namespace zdraw

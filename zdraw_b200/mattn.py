@@ -24,7 +24,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import _lib
-from ._lib import AttnParams, DTYPE_F16, DTYPE_F32, HEAD_DIM, LAYOUT_HEAD_MAJOR, LAYOUT_TOKEN_MAJOR
+from ._lib import AttnParams, DTYPE_F16, DTYPE_F32, HEAD_DIM, LAYOUT_HEAD_MAJOR, LAYOUT_TOKEN_MAJOR, LinearParams
 
 
 class UnsupportedShape(Exception):
@@ -187,6 +187,14 @@ class Context:
             self._h, self._stream_ptr(stream), _ptr(q), _ptr(k), _ptr(v), _ptr(q_w_txt), _ptr(q_w_img),
             _ptr(k_w_txt), _ptr(k_w_img), _ptr(rope_cos), _ptr(rope_sin), _ptr(key_mask), _ptr(out),
             C.byref(params)))
+
+    def linear(self, a, w, c, params: LinearParams, norm_w_txt=None, norm_w_img=None, rope_cos=None,
+               rope_sin=None, stream=None) -> None:
+        """``gemmRunF16A`` (src/klein/zflux2_resident.zig:924-990): c = a @ w.T on device tensors; with
+        ``params.epilogue = 1`` the q/k prologue is applied to the accumulator and c is fp16 head-major."""
+        self._check(self._lib.zdraw_cuda_linear(self._h, self._stream_ptr(stream), _ptr(a), _ptr(w), _ptr(c),
+                                                _ptr(norm_w_txt), _ptr(norm_w_img), _ptr(rope_cos), _ptr(rope_sin),
+                                                C.byref(params)))
 
     def joint_attention_host(self, q, k, v, q_w_txt, q_w_img, k_w_txt, k_w_img, rope_cos, rope_sin, out,
                              params: AttnParams, key_mask=None) -> None:
