@@ -312,6 +312,49 @@ def main():
     ms_prologue = timed(prologue)
     ms_attention = timed(attention)
 
+    # ---- the projection GEMM either side of attention (Q projection with the prologue as its
+    #      epilogue; a plain f16 projection such as V or the output projection), same token count
+    projection = None
+    hidden = w.heads * 128
+    if not by_heads and hidden % 256 == 0:
+        from zdraw_b200._lib import LinearParams
+
+        m_rows = w.batch * w.tokens
+        gemm_bytes = 2 * (2 * m_rows * hidden + hidden * hidden)
+        g_sets = max(2, int(2 * L2_BYTES // gemm_bytes) + 1)
+        g = torch.Generator(device="cuda").manual_seed(w.seed + 7)
+        acts = [torch.randn((m_rows, hidden), device="cuda", generator=g).half() for _ in range(g_sets)]
+        wts = [(torch.randn((hidden, hidden), device="cuda", generator=g) * hidden ** -0.5).half()
+               for _ in range(g_sets)]
+        c_plain = [torch.empty((m_rows, hidden), dtype=torch.float16, device="cuda") for _ in range(g_sets)]
+        c_qk = [torch.empty((w.batch, w.heads, w.tokens, 128), dtype=torch.float16, device="cuda")
+                for _ in range(g_sets)]
+        lp_plain = LinearParams(m=m_rows, n=hidden, k=hidden, a_dtype=1, w_dtype=1, c_dtype=1, epilogue=0)
+        lp_qk = LinearParams(m=m_rows, n=hidden, k=hidden, a_dtype=1, w_dtype=1, c_dtype=1, epilogue=1,
+                             tokens=w.tokens, heads=w.heads, txt_tokens=p.txt_tokens, norm_eps=p.norm_eps,
+                             rope_batch_stride=p.rope_batch_stride)
+
+        def gemm_plain(i):
+            j = i % g_sets
+            ctx.linear(acts[j], wts[j], c_plain[j], lp_plain, stream=stream)
+
+        def gemm_qk(i):
+            j = i % g_sets
+            ctx.linear(acts[j], wts[j], c_qk[j], lp_qk, x0["q_w_txt"], x0["q_w_img"], x0["rope_cos"], x0["rope_sin"],
+                       stream=stream)
+
+        ms_gp, ms_gq = timed(gemm_plain), timed(gemm_qk)
+        gemm_flops = 2.0 * m_rows * hidden * hidden
+        projection = {
+            "kernel": "linear_kernel", "m": m_rows, "n": hidden, "k": hidden, "bound": "tensor",
+            "l2": f"operands rotate over {g_sets} sets ({g_sets * gemm_bytes / 1e6:.0f} MB)",
+            "plain_f16": {"ms_per_launch": ms_gp, "achieved": gemm_flops / ms_gp / 1e9, "unit": "TFLOP/s"},
+            "qk_epilogue": {"ms_per_launch": ms_gq, "achieved": gemm_flops / ms_gq / 1e9, "unit": "TFLOP/s"},
+        }
+        del acts, wts, c_plain, c_qk
+        if ctx.last_status() != 0:
+            raise SystemExit("the projection kernel reported a non-zero status")
+
     # ---- end to end from pinned host buffers through the host-buffer C-ABI entry point
     xh = workloads.make_inputs(w, "cpu", pin=True)
     p_host = workloads.params(w, heads=hs.count, out_layout=1 if by_heads else 0)
@@ -385,6 +428,11 @@ def main():
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
+        if projection is not None:
+            for leg in ("plain_f16", "qk_epilogue"):
+                projection[leg]["frac"] = projection[leg]["achieved"] / peaks["bf16_tflops"]
+            projection["peak"] = peaks["bf16_tflops"]
+            line["projection"] = projection
         if world == 1 and not args.no_cpu_baseline:
             import oracle
 

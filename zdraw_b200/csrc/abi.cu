@@ -593,7 +593,7 @@ int zdraw_cuda_linear(void* ctx, void* stream, const void* a, const void* w, voi
     la.rope_batch_stride = static_cast<long long>(p->rope_batch_stride);
   }
   ZD_CUDA(cx, cudaSetDevice(cx->device));
-  // Row-major f16 matrices [rows][ld] as tiled tensor maps: boxes of 64 columns x 128 (A) or 256 (W) rows.
+  // Row-major f16 matrices [rows][ld] as tiled tensor maps: boxes of 64 columns x 128 rows.
   CUtensorMap tm_a, tm_w;
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   auto encode = [&](CUtensorMap* tm, const void* base_ptr, uint64_t rows, long long ld, uint32_t box_rows) {
@@ -605,7 +605,7 @@ int zdraw_cuda_linear(void* ctx, void* stream, const void* a, const void* w, voi
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
-  if (encode(&tm_a, a, p->m, ld_a, 128) != CUDA_SUCCESS || encode(&tm_w, w, p->n, ld_w, 256) != CUDA_SUCCESS)
+  if (encode(&tm_a, a, p->m, ld_a, 128) != CUDA_SUCCESS || encode(&tm_w, w, p->n, ld_w, 128) != CUDA_SUCCESS)
     return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
   ZD_CUDA(cx, zdraw::launch_linear(static_cast<cudaStream_t>(stream), tm_a, tm_w, la, cx->sm_count));
   return ZDRAW_CUDA_OK;

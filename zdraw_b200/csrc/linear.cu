@@ -10,11 +10,17 @@
 //            by krms_rope_hm (src/klein/zflux2_glue_shader.zig:95-122) without the f32 q/k
 //            round trip through memory that the reference makes between the two.
 //
-// Persistent, warp-specialised: warp 0 feeds 128B-swizzled A (128 x 64) and W (256 x 64) tiles
-// through a 4-stage ring with TMA (no multicast), warp 1 issues M128 N256 K16 MMAs, warps 4-11
-// run the epilogue (warps 4-7 columns [0,128), warps 8-11 columns [128,256) of a row) out of one
-// of two 256-column accumulators while the tensor core fills the other. Tiles are assigned statically (tile = blockIdx.x + i * gridDim.x) and K is walked in
-// order, so results are bit-identical run to run.
+// Persistent, warp-specialised, one CTA pair (cluster of two, tcgen05 cta_group::2) per 256 x 256
+// tile of C: each CTA stages its own 128 rows of A and 128 of the tile's 256 rows of W
+// (128B-swizzled 64-wide K slices, 32 KB per stage, 6 stages, TMA without multicast), the
+// even-rank CTA's warp 1 issues M256 N256 K16 MMAs that read A from each CTA's own shared memory
+// and W from both, and each CTA ends up with its 128 rows x 256 columns of the accumulator in
+// its own TMEM. Pairing halves the bytes each SM pulls from L2 per MMA compared with a lone CTA
+// on a 128 x 256 tile, which is what keeps the tensor pipe fed. Warps 4-11 of both CTAs run the
+// epilogue (warps 4-7 columns [0,128), warps 8-11 columns [128,256) of a row) out of one of two
+// 256-column accumulators while the tensor cores fill the other. Tiles are assigned statically
+// (pair tile = pair + i * pairs) and K is walked in order, so results are bit-identical run to
+// run.
 #include "linear.cuh"
 
 #include <cuda.h>
@@ -27,26 +33,30 @@ namespace zdraw {
 
 namespace {
 
-constexpr int kTM = 128;                 // rows of C per tile
+constexpr int kTM = 128;                 // rows of C per CTA (256 per pair)
 constexpr int kTN = 256;                 // columns of C per tile (two heads of 128)
 constexpr int kTK = 64;                  // K per stage: one 128-byte swizzled row of f16
-constexpr int kStages = 4;
-constexpr int kABytes = kTM * kTK * 2;   // 16 KB
-constexpr int kBBytes = kTN * kTK * 2;   // 32 KB
+constexpr int kStages = 6;
+constexpr int kABytes = kTM * kTK * 2;        // 16 KB: this CTA's rows of A
+constexpr int kBBytes = (kTN / 2) * kTK * 2;  // 16 KB: this CTA's half of the tile's rows of W
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kThreads = 384;            // warps 0-3 control, 4-11 epilogue (two warps per accumulator row)
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 constexpr float kHalfMax = 65504.0f;
 
 constexpr int kOffBar = kStages * kStageBytes;
-constexpr int kBarFull = 0;                    // [kStages]
-constexpr int kBarEmpty = kStages;             // [kStages]
-constexpr int kBarAccFull = 2 * kStages;       // [2]
-constexpr int kBarAccEmpty = 2 * kStages + 2;  // [2]
+constexpr int kBarFull = 0;                    // [kStages] even CTA only: both CTAs' bytes of a stage landed
+constexpr int kBarEmpty = kStages;             // [kStages] both CTAs: the MMAs reading a stage finished
+constexpr int kBarAccFull = 2 * kStages;       // [2] both CTAs: an accumulator is complete
+constexpr int kBarAccEmpty = 2 * kStages + 2;  // [2] even CTA only: both CTAs' epilogues drained it
 constexpr int kBarDrain = 2 * kStages + 4;     // [1]
 constexpr int kNumBars = 2 * kStages + 5;
 constexpr int kOffFlags = kOffBar + kNumBars * 8;
-constexpr int kSmemBytes = kOffFlags + 16;
+// qk epilogue: per epilogue warp, 16 columns of 32 tokens' cos and sin rows (2 x 32 x 64 bytes).
+constexpr int kTabBytesPerWarp = 2 * 32 * 64;
+constexpr int kOffTab = (kOffFlags + 16 + 127) / 128 * 128;
+constexpr int kSmemBytes = kOffTab + 8 * kTabBytesPerWarp;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
 constexpr uint32_t kStLinear = 1u << 4;  // status bit: a bounded wait in this kernel gave up
 
@@ -86,13 +96,17 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();  // 0: issues the pair's MMAs
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int tiles_n = a.n / kTN;
-  const int tiles_m = (a.m + kTM - 1) / kTM;
+  const int tiles_m = (a.m + 2 * kTM - 1) / (2 * kTM);  // pair tiles: 256 rows
   const int n_tiles = tiles_m * tiles_n;
   const int k_steps = a.k / kTK;
 
   if (threadIdx.x == 0) {
-    flags[0] = (*reinterpret_cast<volatile uint32_t*>(a.status) != 0u) ? 1u : 0u;
+    // Both CTAs of a pair take every collective step below whatever happens, so a failed wait
+    // only empties the role loops; the shared-memory base is the same in both CTAs.
+    flags[0] = 0u;
     if ((base & 1023u) != 0u) {  // the swizzled tiles need a 1024-byte aligned base
       flags[0] = 1u;
       atomicOr(a.status, kStLinear);
@@ -104,20 +118,21 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(kBarAccFull + b), 1);
-      mbar_init(bar(kBarAccEmpty + b), 256);
+      mbar_init(bar(kBarAccEmpty + b), 16);  // one arrival per epilogue warp of either CTA
     }
     mbar_init(bar(kBarDrain), 1);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
   __syncthreads();
-  if (*abort_flag) return;
   if (warp == 1) {
-    tmem_alloc(base + kOffFlags + 4, 512);
-    tmem_relinquish();
+    tmem_alloc_pair(base + kOffFlags + 4, 512);
+    tmem_relinquish_pair();
   }
   tc_fence_before();
-  __syncthreads();
+  // The peer's barriers must be initialised before anything of this CTA can signal them.
+  cluster_arrive();
+  cluster_wait();
   tc_fence_after();
   const uint32_t tmem_base = flags[1];
   grid_dependency_wait();
@@ -128,19 +143,23 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
       tma_prefetch_desc(&tm_a);
       tma_prefetch_desc(&tm_w);
       uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      bool ok = *abort_flag == 0u;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
         // Consecutive tiles share the W block (tile_n) and walk down the rows: W stays in L2.
         const int tile_n = tile / tiles_m, tile_m = tile % tiles_m;
+        const int row_a = (2 * tile_m + static_cast<int>(rank)) * kTM;
+        const int row_w = tile_n * kTN + static_cast<int>(rank) * (kTN / 2);
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const uint32_t stage = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
           ok = wait_bar(bar(kBarEmpty + stage), phase ^ 1u, abort_flag, a.status);
           if (!ok) break;
           const uint32_t dst = base + stage * kStageBytes;
-          mbar_arrive_expect_tx(bar(kBarFull + stage), kStageBytes);
-          tma_load_4d(dst, &tm_a, bar(kBarFull + stage), ks * kTK, tile_m * kTM, 0, 0);
-          tma_load_4d(dst + kABytes, &tm_w, bar(kBarFull + stage), ks * kTK, tile_n * kTN, 0, 0);
+          // Both CTAs' bytes are counted on the even CTA's barrier, which expects all of them.
+          const uint32_t full = cluster_map(bar(kBarFull + stage), 0);
+          if (rank == 0) mbar_arrive_expect_tx(bar(kBarFull + stage), 2 * kStageBytes);
+          tma_load_4d_pair(dst, &tm_a, full, ks * kTK, row_a, 0, 0);
+          tma_load_4d_pair(dst + kABytes, &tm_w, full, ks * kTK, row_w, 0, 0);
         }
       }
       if (!ok) {
@@ -150,12 +169,12 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(kTM, kTN, 0, 0);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(2 * kTM, kTN, 0, 0);
       uint32_t it = 0;
       int local = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++local) {
+      bool ok = *abort_flag == 0u;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
         const int b = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1);
         // The epilogue warps must have drained this accumulator (first use passes at once).
@@ -173,14 +192,14 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
           const uint64_t desc_b = smem_desc_sw128(a_addr + kABytes, 16, 1024);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ss(d_tmem, desc_a + 2u * kk, desc_b + 2u * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(bar(kBarEmpty + stage));
+            umma_ss_pair(d_tmem, desc_a + 2u * kk, desc_b + 2u * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+          umma_commit_pair(bar(kBarEmpty + stage), 3);  // both CTAs' producers may refill the stage
         }
         if (!ok) break;
-        umma_commit(bar(kBarAccFull + b));
+        umma_commit_pair(bar(kBarAccFull + b), 3);  // both CTAs' epilogues may read their rows
       }
       if (!ok) {
-        umma_commit(bar(kBarDrain));
+        umma_commit_pair(bar(kBarDrain), 1);
         const uint64_t t0 = globaltimer_ns();
         while (!mbar_try_wait(bar(kBarDrain), 0) && globaltimer_ns() - t0 < kWaitLimitNs) {
         }
@@ -194,9 +213,9 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     int local = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++local) {
-      const int tile_n = tile / tiles_m, tile_m = tile % tiles_m;
+    bool ok = __all_sync(0xffffffffu, *abort_flag == 0u);  // warp-uniform
+    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
+      const int tile_n = tile / tiles_m, tile_m = 2 * (tile % tiles_m) + static_cast<int>(rank);
       const int b = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
       ok = __all_sync(0xffffffffu, wait_bar(bar(kBarAccFull + b), use & 1u, abort_flag, a.status));
@@ -237,8 +256,12 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
         const int tok = static_cast<int>(mm % a.tokens);
         const int img = static_cast<int>(mm / a.tokens);
         const float* w = (tok < a.txt_tokens) ? a.w_txt : a.w_img;
-        const float* cos_row = a.rope_cos + static_cast<long long>(img) * a.rope_batch_stride + static_cast<long long>(tok) * 128;
-        const float* sin_row = a.rope_sin + static_cast<long long>(img) * a.rope_batch_stride + static_cast<long long>(tok) * 128;
+        // Offsets into the cos/sin tables of the rows this lane fetches for the warp (see pass 2).
+        const long long my_off = static_cast<long long>(img) * a.rope_batch_stride + static_cast<long long>(tok) * 128;
+        long long roff[4];
+#pragma unroll
+        for (int it = 0; it < 4; ++it) roff[it] = __shfl_sync(0xffffffffu, my_off, it * 8 + (lane >> 2)) + 4 * (lane & 3);
+        float4* tab = reinterpret_cast<float4*>(smem_raw + kOffTab + (warp - 4) * kTabBytesPerWarp);
         {
           const int head = tile_n * 2 + hh;
           const uint32_t t_head = t_acc + 128u * hh;
@@ -258,45 +281,76 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
             }
           }
           const float inv = 1.0f / sqrtf(((ss0 + ss1) + (ss2 + ss3)) * (1.0f / 128.0f) + a.norm_eps);
-          // pass 2: x inv w, pair rotation, clamp, fp16, head-major store
+          // pass 2: x inv w, pair rotation, clamp, fp16, head-major store, 16 columns at a time.
+          // A thread owns one token, and its cos/sin row is 512 bytes away from its neighbour's,
+          // so the warp fetches 8 rows x 64 bytes per load instruction (lane -> row lane/4,
+          // 16-byte piece lane%4), parks them in shared memory and each thread reads its own row
+          // back. The next 16 columns are in flight while these are rotated.
           __half* dst = static_cast<__half*>(a.c) +
                         ((static_cast<long long>(img) * a.heads + head) * a.tokens + tok) * 128;
+          float4 pc[4], ps[4];
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            pc[it] = __ldg(reinterpret_cast<const float4*>(a.rope_cos + roff[it]));
+            ps[it] = __ldg(reinterpret_cast<const float4*>(a.rope_sin + roff[it]));
+          }
 #pragma unroll 1
-          for (int ch = 0; ch < 4; ++ch) {
-            uint32_t x[32];
-            tmem_ld_x32(t_head + 32u * ch, x);
-            tmem_wait_ld();
-            if (live) {
-              uint32_t out[16];
+          for (int sub = 0; sub < 8; ++sub) {
+            __syncwarp();  // every lane has read the previous 16 columns out of shared memory
 #pragma unroll
-              for (int q4 = 0; q4 < 8; ++q4) {  // four columns = two pairs at a time
-                const int col = 32 * ch + 4 * q4;
-                const float4 wv = __ldg(reinterpret_cast<const float4*>(w + col));
-                const float4 cv = __ldg(reinterpret_cast<const float4*>(cos_row + col));
-                const float4 sv = __ldg(reinterpret_cast<const float4*>(sin_row + col));
-                const float x0 = __uint_as_float(x[4 * q4]) * inv * wv.x;
-                const float x1 = __uint_as_float(x[4 * q4 + 1]) * inv * wv.y;
-                const float x2 = __uint_as_float(x[4 * q4 + 2]) * inv * wv.z;
-                const float x3 = __uint_as_float(x[4 * q4 + 3]) * inv * wv.w;
-                out[2 * q4] = pack_clamped(x0 * cv.x - x1 * sv.x, x1 * cv.y + x0 * sv.y);
-                out[2 * q4 + 1] = pack_clamped(x2 * cv.z - x3 * sv.z, x3 * cv.w + x2 * sv.w);
+            for (int it = 0; it < 4; ++it) {
+              const int r = it * 8 + (lane >> 2);
+              const int idx = r * 4 + ((lane & 3) ^ ((r >> 1) & 3));
+              tab[idx] = pc[it];
+              tab[128 + idx] = ps[it];
+            }
+            __syncwarp();
+            if (sub < 7) {
+#pragma unroll
+              for (int it = 0; it < 4; ++it) {
+                pc[it] = __ldg(reinterpret_cast<const float4*>(a.rope_cos + roff[it] + 16 * (sub + 1)));
+                ps[it] = __ldg(reinterpret_cast<const float4*>(a.rope_sin + roff[it] + 16 * (sub + 1)));
               }
-              uint4* d4 = reinterpret_cast<uint4*>(dst + 32 * ch);
+            }
+            uint32_t x[16];
+            tmem_ld_x16(t_head + 16u * sub, x);
+            tmem_wait_ld();
+            uint32_t out[8];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) d4[i] = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+            for (int q4 = 0; q4 < 4; ++q4) {  // four columns = two pairs at a time
+              const int idx = lane * 4 + (q4 ^ ((lane >> 1) & 3));
+              const float4 cv = tab[idx];
+              const float4 sv = tab[128 + idx];
+              const float4 wv = __ldg(reinterpret_cast<const float4*>(w + 16 * sub + 4 * q4));
+              const float x0 = __uint_as_float(x[4 * q4]) * inv * wv.x;
+              const float x1 = __uint_as_float(x[4 * q4 + 1]) * inv * wv.y;
+              const float x2 = __uint_as_float(x[4 * q4 + 2]) * inv * wv.z;
+              const float x3 = __uint_as_float(x[4 * q4 + 3]) * inv * wv.w;
+              out[2 * q4] = pack_clamped(x0 * cv.x - x1 * sv.x, x1 * cv.y + x0 * sv.y);
+              out[2 * q4 + 1] = pack_clamped(x2 * cv.z - x3 * sv.z, x3 * cv.w + x2 * sv.w);
+            }
+            if (live) {
+              uint4* d4 = reinterpret_cast<uint4*>(dst + 16 * sub);
+              d4[0] = make_uint4(out[0], out[1], out[2], out[3]);
+              d4[1] = make_uint4(out[4], out[5], out[6], out[7]);
             }
           }
         }
       }
-      // This accumulator may be overwritten by the tile after next.
+      // This accumulator may be overwritten by the tile after next, once every epilogue warp of
+      // the pair has said so to the even CTA.
       tc_fence_before();
-      mbar_arrive(bar(kBarAccEmpty + b));
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(cluster_map(bar(kBarAccEmpty + b), 0));
     }
   }
 
+  // Neither CTA may leave while the other can still read its shared memory or signal its
+  // barriers.
   tc_fence_before();
-  __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  cluster_arrive();
+  cluster_wait();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 
 }  // namespace
@@ -307,18 +361,36 @@ cudaError_t linear_configure() {
 
 cudaError_t launch_linear(cudaStream_t stream, const CUtensorMap& tm_a, const CUtensorMap& tm_w,
                           const LinearArgs& args, int sm_count) {
-  const int n_tiles = ((args.m + kTM - 1) / kTM) * (args.n / kTN);
-  const int grid = n_tiles < sm_count ? n_tiles : sm_count;
+  const int n_tiles = ((args.m + 2 * kTM - 1) / (2 * kTM)) * (args.n / kTN);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
+  // One resident CTA pair per two SMs; how many pairs the device can hold at once is asked once
+  // per device (a pair needs two SMs of one GPC).
+  static int pairs_of_device[64] = {};
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  int pairs = (device >= 0 && device < 64) ? pairs_of_device[device] : 0;
+  if (pairs == 0) {
+    cfg.gridDim = dim3(2 * (sm_count / 2));
+    err = cudaOccupancyMaxActiveClusters(&pairs, linear_kernel, &cfg);
+    if (err != cudaSuccess) return err;
+    if (pairs <= 0) return cudaErrorLaunchOutOfResources;
+    if (pairs > sm_count / 2) pairs = sm_count / 2;
+    if (device >= 0 && device < 64) pairs_of_device[device] = pairs;
+  }
+  cfg.gridDim = dim3(2 * (n_tiles < pairs ? n_tiles : pairs));
   return cudaLaunchKernelEx(&cfg, linear_kernel, tm_a, tm_w, args);
 }
 

@@ -11,7 +11,7 @@ constexpr int kEpiloguePlain = 0;
 constexpr int kEpilogueQk = 1;
 
 // C[m, n] = A[m, k] * W[n, k]^T. A and W are reached through tensor maps (f16, 128-byte swizzle,
-// boxes 64 x 128 and 64 x 256). n % 256 == 0, k % 64 == 0.
+// boxes of 64 columns x 128 rows). n % 256 == 0, k % 64 == 0.
 struct LinearArgs {
   int m, n, k;
   int epilogue;  // kEpiloguePlain | kEpilogueQk

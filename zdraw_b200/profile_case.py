@@ -1,6 +1,7 @@
 """Runs the joint-attention path a few times on one synthetic workload (for profilers).
 
     python -m zdraw_b200.profile_case --workload klein_1024 --iters 4
+    python -m zdraw_b200.profile_case --workload klein_1024 --iters 4 --case linear_qk   (or linear_plain)
 
 One untimed call, then `iters` timed ones. Launches per call: qk_norm_rope_kernel, attn_fwd_kernel (plus mask_prepare_kernel with a key
 mask and cast_f32_to_f16_kernel for f32 inputs). Prints the mean device time per iteration.
@@ -19,6 +20,9 @@ def main() -> None:
     ap.add_argument("--workload", default="klein_1024", choices=sorted(workloads.WORKLOADS))
     ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch")
+    ap.add_argument("--case", default="joint", choices=["joint", "linear_plain", "linear_qk"],
+                    help="joint: prologue + attention; linear_*: one projection GEMM (linear_kernel) of the "
+                         "workload's token count and hidden size, plain f16 store or fused q/k epilogue")
     args = ap.parse_args()
     w = workloads.WORKLOADS[args.workload]
     if args.batch:
@@ -32,6 +36,29 @@ def main() -> None:
         ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
                             x["rope_cos"], x["rope_sin"], out, p, key_mask=x["key_mask"])
 
+    flops = w.flops
+    if args.case != "joint":
+        from ._lib import LinearParams
+
+        m, hidden = w.batch * w.tokens, w.heads * 128
+        a = torch.randn((m, hidden), device="cuda").half()
+        wt = (torch.randn((hidden, hidden), device="cuda") * hidden ** -0.5).half()
+        flops = 2.0 * m * hidden * hidden
+        if args.case == "linear_plain":
+            c = torch.empty((m, hidden), dtype=torch.float16, device="cuda")
+            lp = LinearParams(m=m, n=hidden, k=hidden, a_dtype=1, w_dtype=1, c_dtype=1, epilogue=0)
+
+            def call():
+                ctx.linear(a, wt, c, lp)
+        else:
+            c = torch.empty((w.batch, w.heads, w.tokens, 128), dtype=torch.float16, device="cuda")
+            lp = LinearParams(m=m, n=hidden, k=hidden, a_dtype=1, w_dtype=1, c_dtype=1, epilogue=1, tokens=w.tokens,
+                              heads=w.heads, txt_tokens=p.txt_tokens, norm_eps=p.norm_eps,
+                              rope_batch_stride=p.rope_batch_stride)
+
+            def call():
+                ctx.linear(a, wt, c, lp, x["q_w_txt"], x["q_w_img"], x["rope_cos"], x["rope_sin"])
+
     call()  # first call sizes the context scratch
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
@@ -42,7 +69,7 @@ def main() -> None:
     torch.cuda.synchronize()
     status = ctx.last_status()
     ms = e0.elapsed_time(e1) / args.iters
-    print(f"{w.name}: {ms:.4f} ms/iter, {w.flops / ms / 1e9:.1f} TFLOP/s, status {status}")
+    print(f"{w.name} ({args.case}): {ms:.4f} ms/iter, {flops / ms / 1e9:.1f} TFLOP/s, status {status}")
     ctx.deinit()
     if status != 0:
         raise SystemExit(1)
