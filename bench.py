@@ -343,13 +343,19 @@ def main():
             ctx.linear(acts[j], wts[j], c_qk[j], lp_qk, x0["q_w_txt"], x0["q_w_img"], x0["rope_cos"], x0["rope_sin"],
                        stream=stream)
 
-        ms_gp, ms_gq = timed(gemm_plain), timed(gemm_qk)
+        def gemm_library(i):  # cuBLAS through torch, same operands: the library figure beside ours
+            j = i % g_sets
+            torch.matmul(acts[j], wts[j].t(), out=c_plain[j])
+
+        ms_gp, ms_gq, ms_gl = timed(gemm_plain), timed(gemm_qk), timed(gemm_library)
         gemm_flops = 2.0 * m_rows * hidden * hidden
         projection = {
             "kernel": "linear_kernel", "m": m_rows, "n": hidden, "k": hidden, "bound": "tensor",
             "l2": f"operands rotate over {g_sets} sets ({g_sets * gemm_bytes / 1e6:.0f} MB)",
             "plain_f16": {"ms_per_launch": ms_gp, "achieved": gemm_flops / ms_gp / 1e9, "unit": "TFLOP/s"},
             "qk_epilogue": {"ms_per_launch": ms_gq, "achieved": gemm_flops / ms_gq / 1e9, "unit": "TFLOP/s"},
+            "cublas_f16": {"ms_per_launch": ms_gl, "achieved": gemm_flops / ms_gl / 1e9, "unit": "TFLOP/s",
+                           "note": "torch.matmul on the same operands, no epilogue; for comparison only"},
         }
         del acts, wts, c_plain, c_qk
         if ctx.last_status() != 0:
@@ -429,7 +435,7 @@ def main():
             "clocks": clocks,
         }
         if projection is not None:
-            for leg in ("plain_f16", "qk_epilogue"):
+            for leg in ("plain_f16", "qk_epilogue", "cublas_f16"):
                 projection[leg]["frac"] = projection[leg]["achieved"] / peaks["bf16_tflops"]
             projection["peak"] = peaks["bf16_tflops"]
             line["projection"] = projection

@@ -113,6 +113,14 @@ class Context {
                                                      rope_sin, key_mask, out, &p));
   }
 
+  // gemmRunF16A (src/klein/zflux2_resident.zig:924-990): c = a * w^T on device buffers; with
+  // p.epilogue = 1 the q/k prologue is applied to the accumulator and c is fp16 head-major.
+  Error linear(void* stream, const void* a, const void* w, void* c, const zdraw_cuda_linear_params& p,
+               const float* norm_w_txt = nullptr, const float* norm_w_img = nullptr,
+               const float* rope_cos = nullptr, const float* rope_sin = nullptr) {
+    return from_code(zdraw_cuda_linear(ctx_, stream, a, w, c, norm_w_txt, norm_w_img, rope_cos, rope_sin, &p));
+  }
+
   uint32_t last_status(void* stream = nullptr) {
     uint32_t st = 0;
     zdraw_cuda_last_status(ctx_, stream, &st);

@@ -38,6 +38,31 @@ comptime {
     if (@sizeOf(AttnParams) != 104) @compileError("zdraw_cuda_attn_params size drifted");
 }
 
+// zdraw_cuda_linear_params: the projection GEMM either side of attention (gemmRunF16A,
+// src/klein/zflux2_resident.zig:924-990); epilogue 1 applies rmsRopeHm to the accumulator.
+pub const LinearParams = extern struct {
+    m: u32,
+    n: u32,
+    k: u32,
+    a_dtype: u32 = dtype_f16,
+    w_dtype: u32 = dtype_f16,
+    c_dtype: u32 = dtype_f16,
+    epilogue: u32 = 0,
+    reserved: u32 = 0,
+    ld_a: u64 = 0,
+    ld_w: u64 = 0,
+    ld_c: u64 = 0,
+    tokens: u32 = 0,
+    heads: u32 = 0,
+    txt_tokens: u32 = 0,
+    norm_eps: f32 = 0.0,
+    rope_batch_stride: u64 = 0,
+};
+
+comptime {
+    if (@sizeOf(LinearParams) != 80) @compileError("zdraw_cuda_linear_params size drifted");
+}
+
 pub extern fn zdraw_cuda_attn_params_size() usize;
 pub extern fn zdraw_cuda_attn_create(device: c_int, ctx: *?*anyopaque) c_int;
 pub extern fn zdraw_cuda_attn_destroy(ctx: *anyopaque) c_int;
@@ -82,6 +107,59 @@ pub extern fn zdraw_cuda_joint_attention(
     key_mask: ?[*]const f32,
     o: *anyopaque,
     params: *const AttnParams,
+) c_int;
+pub extern fn zdraw_cuda_linear(
+    ctx: *anyopaque,
+    stream: ?*anyopaque,
+    a_f16: *const anyopaque,
+    w_f16: *const anyopaque,
+    c: *anyopaque,
+    norm_w_txt: ?[*]const f32,
+    norm_w_img: ?[*]const f32,
+    rope_cos: ?[*]const f32,
+    rope_sin: ?[*]const f32,
+    params: *const LinearParams,
+) c_int;
+pub extern fn zdraw_cuda_attention_host(
+    ctx: *anyopaque,
+    q: *const anyopaque,
+    k: *const anyopaque,
+    v: *const anyopaque,
+    key_mask: ?[*]const f32,
+    o: *anyopaque,
+    params: *const AttnParams,
+) c_int;
+pub extern fn zdraw_cuda_joint_attention_host(
+    ctx: *anyopaque,
+    q: *const anyopaque,
+    k: *const anyopaque,
+    v: *const anyopaque,
+    q_w_txt: [*]const f32,
+    q_w_img: [*]const f32,
+    k_w_txt: [*]const f32,
+    k_w_img: [*]const f32,
+    rope_cos: [*]const f32,
+    rope_sin: [*]const f32,
+    key_mask: ?[*]const f32,
+    o: *anyopaque,
+    params: *const AttnParams,
+) c_int;
+// No counterpart in the reference: the joint call without any device allocation (fixed 64 MiB
+// scratch inside the library; fp16 inputs, no key mask; calls must not overlap).
+pub extern fn zdraw_cuda_joint_attention_static(
+    stream: ?*anyopaque,
+    q: *const anyopaque,
+    k: *const anyopaque,
+    v: *const anyopaque,
+    q_w_txt: [*]const f32,
+    q_w_img: [*]const f32,
+    k_w_txt: [*]const f32,
+    k_w_img: [*]const f32,
+    rope_cos: [*]const f32,
+    rope_sin: [*]const f32,
+    o: *anyopaque,
+    params: *const AttnParams,
+    error_text: ?*[*:0]const u8,
 ) c_int;
 pub extern fn zdraw_cuda_last_status(ctx: *anyopaque, stream: ?*anyopaque, status: *u32) c_int;
 pub extern fn zdraw_cuda_last_error(ctx: ?*anyopaque) [*:0]const u8;
