@@ -199,6 +199,41 @@ def test_joint_tiny_config_f32(ctx, oracle):
     assert np.array_equal(out_h, out.cpu().numpy())
 
 
+@pytest.mark.parametrize("out_layout", [0, 1])
+def test_joint_host_call_in_head_chunks_matches_device_call(ctx, out_layout):
+    """A host-buffer call large enough to be cut into head chunks (4 + 4 + 2 heads, two images,
+    ragged tokens, padded strides, a key mask) gives the bytes of the device call and leaves the
+    padding columns of the host tensors alone."""
+    w = workloads.Workload("chunked_host", "klein", 2, 10, 100, 20, 30, seed=11, masked_text=(40, 100))  # S = 700
+    x = workloads.make_inputs(w, "cuda")
+    ld = w.heads * 128 + 64
+    p = workloads.params(w, ld_q=ld, ld_k=ld, ld_v=ld, ld_o=ld if out_layout == 0 else 0, out_layout=out_layout)
+    wide = {}
+    for name in ("q", "k", "v"):
+        t = torch.zeros((w.batch, w.tokens, ld), dtype=torch.float16, device="cuda")
+        t[:, :, : w.heads * 128] = x[name].reshape(w.batch, w.tokens, -1)
+        wide[name] = t
+    if out_layout == 0:
+        out_d = torch.zeros((w.batch, w.tokens, ld), dtype=torch.float16, device="cuda")
+    else:
+        out_d = torch.zeros((w.batch, w.heads, w.tokens, 128), dtype=torch.float16, device="cuda")
+    small = (x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"])
+    ctx.joint_attention(wide["q"], wide["k"], wide["v"], *small, out_d, p, key_mask=x["key_mask"])
+    torch.cuda.synchronize()
+    assert ctx.last_status() == 0
+    host = {k: v.cpu().numpy() for k, v in wide.items()}
+    out_h = np.full(tuple(out_d.shape), np.float16(7.0), np.float16)
+    ctx.joint_attention_host(host["q"], host["k"], host["v"], *(t.cpu().numpy() for t in small), out_h, p,
+                             key_mask=x["key_mask"].cpu().numpy())
+    got_d = out_d.cpu().numpy()
+    if out_layout == 0:
+        assert np.array_equal(out_h[:, :, : w.heads * 128], got_d[:, :, : w.heads * 128])
+        assert np.all(out_h[:, :, w.heads * 128:] == np.float16(7.0))  # padding columns untouched
+    else:
+        assert np.array_equal(out_h, got_d)
+    assert np.isfinite(out_h.astype(np.float32)).all()
+
+
 def test_pipeline_trace_facility(ctx):
     """zdraw_cuda_attn_set_trace: the instrumented kernel gives the same bytes and monotonic stamps."""
     import ctypes as C

@@ -42,7 +42,12 @@ struct Ctx {
   uint32_t* d_status = nullptr;
   EncodeTiledFn encode = nullptr;
   int sm_count = 0;
-  cudaStream_t host_stream = nullptr;  // used by the host-buffer entry point only
+  cudaStream_t host_stream = nullptr;  // kernels of the host-buffer entry points
+  // Host-buffer joint call: copies in and out run on their own streams, one event pair per head
+  // chunk, so the PCIe transfers of one chunk overlap the kernels and the transfers of others.
+  cudaStream_t in_stream = nullptr, out_stream = nullptr;
+  static constexpr int kMaxChunks = 16;
+  cudaEvent_t ev_in[kMaxChunks] = {}, ev_done[kMaxChunks] = {};
   unsigned long long* d_trace = nullptr;  // caller's trace buffer while pipeline tracing is on (debugging)
   // Grow-only scratch (device memory).
   Buf q16, k16, v16, tile_list;
@@ -381,6 +386,12 @@ int zdraw_cuda_attn_destroy(void* ctx) {
     if (b->p) cudaFree(b->p);
   if (c->d_status) cudaFree(c->d_status);
   if (c->host_stream) cudaStreamDestroy(c->host_stream);
+  if (c->in_stream) cudaStreamDestroy(c->in_stream);
+  if (c->out_stream) cudaStreamDestroy(c->out_stream);
+  for (int i = 0; i < Ctx::kMaxChunks; ++i) {
+    if (c->ev_in[i]) cudaEventDestroy(c->ev_in[i]);
+    if (c->ev_done[i]) cudaEventDestroy(c->ev_done[i]);
+  }
   c->magic = 0;
   delete c;
   return ZDRAW_CUDA_OK;
@@ -457,25 +468,86 @@ int zdraw_cuda_joint_attention_host(void* ctx, const void* q, const void* k, con
       (rc = ensure(c, c->st_sin, rope_elems * sizeof(float))))
     return rc;
   if (p->has_key_mask && (rc = ensure(c, c->st_mask, mask_elems * sizeof(float)))) return rc;
-  cudaStream_t st = c->host_stream;
+  // Lazily made once per context: the copy streams and one event pair per chunk.
+  if (!c->in_stream) {
+    ZD_CUDA(c, cudaStreamCreateWithFlags(&c->in_stream, cudaStreamNonBlocking));
+    ZD_CUDA(c, cudaStreamCreateWithFlags(&c->out_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < Ctx::kMaxChunks; ++i) {
+      ZD_CUDA(c, cudaEventCreateWithFlags(&c->ev_in[i], cudaEventDisableTiming));
+      ZD_CUDA(c, cudaEventCreateWithFlags(&c->ev_done[i], cudaEventDisableTiming));
+    }
+  }
+  // Heads are independent, so the call is cut into head chunks: while chunk i is being computed,
+  // chunk i+1 is on its way in and chunk i-1 on its way out (PCIe is full duplex and the whole
+  // call is bound by it). A chunk is a column slice of the token-major tensors: strided 2-D
+  // copies with rows of at least 1 KB. Small calls stay in one piece.
+  const size_t total_in = (q_bytes + k_bytes + v_bytes);
+  int per_chunk = s.heads;
+  if (total_in >= (8u << 20)) {
+    const int min_heads = static_cast<int>(1024 / (kHeadDim * in_sz));  // 4 heads of f16, 2 of f32
+    per_chunk = (s.heads + Ctx::kMaxChunks - 1) / Ctx::kMaxChunks;
+    if (per_chunk < min_heads) per_chunk = min_heads;
+    if (per_chunk > s.heads) per_chunk = s.heads;
+  }
+  const int n_chunks = (s.heads + per_chunk - 1) / per_chunk;
+  cudaStream_t st = c->host_stream, st_in = c->in_stream, st_out = c->out_stream;
   float* w = static_cast<float*>(c->st_w.p);
-  ZD_CUDA(c, cudaMemcpyAsync(c->st_q.p, q, q_bytes, cudaMemcpyHostToDevice, st));
-  ZD_CUDA(c, cudaMemcpyAsync(c->st_k.p, k, k_bytes, cudaMemcpyHostToDevice, st));
-  ZD_CUDA(c, cudaMemcpyAsync(c->st_v.p, v, v_bytes, cudaMemcpyHostToDevice, st));
-  ZD_CUDA(c, cudaMemcpyAsync(w, q_w_txt, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st));
-  ZD_CUDA(c, cudaMemcpyAsync(w + kHeadDim, q_w_img, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st));
-  ZD_CUDA(c, cudaMemcpyAsync(w + 2 * kHeadDim, k_w_txt, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st));
-  ZD_CUDA(c, cudaMemcpyAsync(w + 3 * kHeadDim, k_w_img, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st));
-  ZD_CUDA(c, cudaMemcpyAsync(c->st_cos.p, rope_cos, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st));
-  ZD_CUDA(c, cudaMemcpyAsync(c->st_sin.p, rope_sin, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st));
+  ZD_CUDA(c, cudaMemcpyAsync(w, q_w_txt, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st_in));
+  ZD_CUDA(c, cudaMemcpyAsync(w + kHeadDim, q_w_img, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st_in));
+  ZD_CUDA(c, cudaMemcpyAsync(w + 2 * kHeadDim, k_w_txt, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st_in));
+  ZD_CUDA(c, cudaMemcpyAsync(w + 3 * kHeadDim, k_w_img, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st_in));
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_cos.p, rope_cos, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st_in));
+  ZD_CUDA(c, cudaMemcpyAsync(c->st_sin.p, rope_sin, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st_in));
   if (p->has_key_mask)
-    ZD_CUDA(c, cudaMemcpyAsync(c->st_mask.p, key_mask, mask_elems * sizeof(float), cudaMemcpyHostToDevice, st));
-  rc = joint(c, st, c->st_q.p, c->st_k.p, c->st_v.p, w, w + kHeadDim, w + 2 * kHeadDim, w + 3 * kHeadDim,
-             static_cast<const float*>(c->st_cos.p), static_cast<const float*>(c->st_sin.p),
-             static_cast<const float*>(c->st_mask.p), c->st_o.p, p, s);
-  if (rc) return rc;
-  ZD_CUDA(c, cudaMemcpyAsync(o, c->st_o.p, o_bytes, cudaMemcpyDeviceToHost, st));
+    ZD_CUDA(c, cudaMemcpyAsync(c->st_mask.p, key_mask, mask_elems * sizeof(float), cudaMemcpyHostToDevice, st_in));
+  for (int ch = 0; ch < n_chunks; ++ch) {
+    const int h0 = ch * per_chunk;
+    const int hc = (h0 + per_chunk <= s.heads) ? per_chunk : s.heads - h0;
+    Shape sc = s;
+    sc.heads = hc;
+    const size_t width_in = static_cast<size_t>(hc) * kHeadDim * in_sz;
+    const size_t col_in = static_cast<size_t>(h0) * kHeadDim * in_sz;
+    char* dq = static_cast<char*>(c->st_q.p) + col_in;
+    char* dk = static_cast<char*>(c->st_k.p) + col_in;
+    char* dv = static_cast<char*>(c->st_v.p) + col_in;
+    ZD_CUDA(c, cudaMemcpy2DAsync(dq, s.ld_q * in_sz, static_cast<const char*>(q) + col_in, s.ld_q * in_sz, width_in, rows,
+                                 cudaMemcpyHostToDevice, st_in));
+    ZD_CUDA(c, cudaMemcpy2DAsync(dk, s.ld_k * in_sz, static_cast<const char*>(k) + col_in, s.ld_k * in_sz, width_in, rows,
+                                 cudaMemcpyHostToDevice, st_in));
+    ZD_CUDA(c, cudaMemcpy2DAsync(dv, s.ld_v * in_sz, static_cast<const char*>(v) + col_in, s.ld_v * in_sz, width_in, rows,
+                                 cudaMemcpyHostToDevice, st_in));
+    ZD_CUDA(c, cudaEventRecord(c->ev_in[ch], st_in));
+    ZD_CUDA(c, cudaStreamWaitEvent(st, c->ev_in[ch], 0));
+    // Token-major O: the chunk's columns of the full-width staging tensor. Head-major O: the
+    // chunk's [image][hc][token][128] block, chunks laid end to end in the staging buffer.
+    const size_t hm_chunk_elems = static_cast<size_t>(hc) * s.tokens * kHeadDim;
+    char* d_o = static_cast<char*>(c->st_o.p) +
+                (o_hm ? static_cast<size_t>(s.batch) * h0 * s.tokens * kHeadDim : static_cast<size_t>(h0) * kHeadDim) * out_sz;
+    rc = joint(c, st, dq, dk, dv, w, w + kHeadDim, w + 2 * kHeadDim, w + 3 * kHeadDim,
+               static_cast<const float*>(c->st_cos.p), static_cast<const float*>(c->st_sin.p),
+               static_cast<const float*>(c->st_mask.p), d_o, p, sc);
+    if (rc) {
+      cudaStreamSynchronize(st_in);
+      cudaStreamSynchronize(st);
+      cudaStreamSynchronize(st_out);
+      return rc;
+    }
+    ZD_CUDA(c, cudaEventRecord(c->ev_done[ch], st));
+    ZD_CUDA(c, cudaStreamWaitEvent(st_out, c->ev_done[ch], 0));
+    if (o_hm) {
+      char* h_o = static_cast<char*>(o) + static_cast<size_t>(h0) * s.tokens * kHeadDim * out_sz;
+      ZD_CUDA(c, cudaMemcpy2DAsync(h_o, static_cast<size_t>(s.heads) * s.tokens * kHeadDim * out_sz, d_o,
+                                   hm_chunk_elems * out_sz, hm_chunk_elems * out_sz, s.batch, cudaMemcpyDeviceToHost,
+                                   st_out));
+    } else {
+      ZD_CUDA(c, cudaMemcpy2DAsync(static_cast<char*>(o) + static_cast<size_t>(h0) * kHeadDim * out_sz, s.ld_o * out_sz, d_o,
+                                   s.ld_o * out_sz, static_cast<size_t>(hc) * kHeadDim * out_sz, rows,
+                                   cudaMemcpyDeviceToHost, st_out));
+    }
+  }
+  ZD_CUDA(c, cudaStreamSynchronize(st_out));
   ZD_CUDA(c, cudaStreamSynchronize(st));
+  ZD_CUDA(c, cudaStreamSynchronize(st_in));
   uint32_t status = 0;
   ZD_CUDA(c, cudaMemcpy(&status, c->d_status, sizeof(status), cudaMemcpyDeviceToHost));
   if (status != 0) return fail(c, ZDRAW_CUDA_E_DEVICE, "kernel gave up a bounded wait (status 0x%x)", status);
