@@ -231,6 +231,22 @@ ZDRAW_CUDA_API int zdraw_cuda_zimage_rope_table(float *cos_out, float *sin_out, 
                                  float theta);
 
 /*
+ * The same two tables built on the GPU, written to DEVICE memory on the caller's stream, so a
+ * forward pass neither builds them on the CPU nor uploads them (the reference builds them on the
+ * CPU once per forward and uploads: zflux2_dit.zig:125-170 / zflux2_resident.zig:1345-1355;
+ * zrope.zig:28-116). Same arguments, validation and return codes as the host builders; cos_dev /
+ * sin_dev are 16-byte aligned device pointers to [tokens][128] f32. Klein tables equal the host
+ * builder's bit for bit (both evaluate cos/sin in f64); Z-Image tables may differ from the host
+ * builder's f32 cosf/sinf in the last bit.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_klein_rope_table_device(void *ctx, void *stream, float *cos_dev, float *sin_dev,
+                                                      size_t txt_len, size_t grid_h, size_t grid_w, size_t ref_h,
+                                                      size_t ref_w, double theta);
+ZDRAW_CUDA_API int zdraw_cuda_zimage_rope_table_device(void *ctx, void *stream, float *cos_dev, float *sin_dev,
+                                                       size_t img_h, size_t img_w, size_t cap_total,
+                                                       const size_t dims[3], const size_t lens[3], float theta);
+
+/*
  * Reads (and clears) the device status word. 0 = every kernel ran to the end.
  * Non-zero = a kernel gave up a bounded wait and returned early; the output of
  * that call is invalid. Synchronises `stream`. Plays the part of the bridge's

@@ -14,6 +14,7 @@
 #include "../../include/zdraw_cuda.h"
 #include "attention_fwd.cuh"
 #include "linear.cuh"
+#include "rope_table.cuh"
 #include "prologue.cuh"
 
 namespace {
@@ -769,6 +770,74 @@ int zdraw_cuda_zimage_rope_table(float* cos_out, float* sin_out, size_t img_h, s
       col += dims[a];
     }
   }
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_klein_rope_table_device(void* ctx, void* stream, float* cos_dev, float* sin_dev, size_t txt_len,
+                                       size_t grid_h, size_t grid_w, size_t ref_h, size_t ref_w, double theta) {
+  Ctx* c = as_ctx(ctx);
+  if (!c) return ZDRAW_CUDA_E_ARG;
+  if (!cos_dev || !sin_dev || !aligned16(cos_dev) || !aligned16(sin_dev) || !(theta > 0.0))
+    return fail(c, ZDRAW_CUDA_E_ARG, "null or misaligned table pointer, or theta <= 0");
+  if ((grid_h == 0) != (grid_w == 0) || (ref_h == 0) != (ref_w == 0))
+    return fail(c, ZDRAW_CUDA_E_ARG, "InvalidConfig: a grid needs both sides");
+  const size_t total = txt_len + grid_h * grid_w + ref_h * ref_w;
+  if (txt_len > kMaxTokens || grid_h > kMaxTokens || grid_w > kMaxTokens || ref_h > kMaxTokens || ref_w > kMaxTokens ||
+      total > kMaxTokens)
+    return fail(c, ZDRAW_CUDA_DECLINED, "more tokens than the attention kernels take");
+  zdraw::KleinRopeArgs a = {};
+  a.cos_out = cos_dev;
+  a.sin_out = sin_dev;
+  a.txt_len = static_cast<int>(txt_len);
+  a.grid_h = static_cast<int>(grid_h);
+  a.grid_w = static_cast<int>(grid_w);
+  a.ref_h = static_cast<int>(ref_h);
+  a.ref_w = static_cast<int>(ref_w);
+  a.tokens = static_cast<int>(total);
+  // The host builder's frequencies, bit for bit.
+  for (int i = 0; i < 16; ++i) a.freq[i] = 1.0 / std::pow(theta, static_cast<double>(2 * i) / 32.0);
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  ZD_CUDA(c, zdraw::launch_klein_rope_table(static_cast<cudaStream_t>(stream), a));
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_zimage_rope_table_device(void* ctx, void* stream, float* cos_dev, float* sin_dev, size_t img_h,
+                                        size_t img_w, size_t cap_total, const size_t dims[3], const size_t lens[3],
+                                        float theta) {
+  Ctx* c = as_ctx(ctx);
+  if (!c) return ZDRAW_CUDA_E_ARG;
+  if (!cos_dev || !sin_dev || !aligned16(cos_dev) || !aligned16(sin_dev) || !dims || !lens || !(theta > 0.0f))
+    return fail(c, ZDRAW_CUDA_E_ARG, "null or misaligned pointer, or theta <= 0");
+  size_t width = 0;
+  for (int a = 0; a < 3; ++a) {
+    if (dims[a] == 0 || lens[a] == 0 || dims[a] % 2 != 0) return fail(c, ZDRAW_CUDA_E_ARG, "InvalidConfig: axis sizes");
+    width += dims[a];
+  }
+  if (width != kHeadDim) return fail(c, ZDRAW_CUDA_E_ARG, "InvalidConfig: axis sizes do not add up to 128");
+  if (img_h > kMaxTokens || img_w > kMaxTokens || cap_total > kMaxTokens || img_h * img_w + cap_total > kMaxTokens)
+    return fail(c, ZDRAW_CUDA_DECLINED, "more tokens than the attention kernels take");
+  // BadPosition, as the host builder finds it token by token: the largest position on each axis.
+  const size_t n_img = img_h * img_w;
+  if (n_img > 0 && (cap_total + 1 >= lens[0] || img_h - 1 >= lens[1] || img_w - 1 >= lens[2]))
+    return fail(c, ZDRAW_CUDA_E_ARG, "BadPosition: image position beyond the axis length");
+  if (cap_total > 0 && cap_total >= lens[0]) return fail(c, ZDRAW_CUDA_E_ARG, "BadPosition: caption position beyond the axis length");
+  zdraw::ZimageRopeArgs a = {};
+  a.cos_out = cos_dev;
+  a.sin_out = sin_dev;
+  a.img_h = static_cast<int>(img_h);
+  a.img_w = static_cast<int>(img_w);
+  a.cap_total = static_cast<int>(cap_total);
+  a.tokens = static_cast<int>(n_img + cap_total);
+  const float neg_log_theta = -std::log(theta);
+  int pair = 0;
+  for (int ax = 0; ax < 3; ++ax)
+    for (size_t pr = 0; pr < dims[ax] / 2; ++pr, ++pair) {
+      const float power = 2.0f * static_cast<float>(pr) / static_cast<float>(dims[ax]);
+      a.freq[pair] = std::exp(neg_log_theta * power);  // the host builder's f32 frequency
+      a.axis[pair] = static_cast<unsigned char>(ax);
+    }
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  ZD_CUDA(c, zdraw::launch_zimage_rope_table(static_cast<cudaStream_t>(stream), a));
   return ZDRAW_CUDA_OK;
 }
 

@@ -174,6 +174,42 @@ pub extern fn zdraw_cuda_klein_rope_table(
     theta: f64,
 ) c_int;
 
+pub extern fn zdraw_cuda_zimage_rope_table(
+    cos_out: [*]f32,
+    sin_out: [*]f32,
+    img_h: usize,
+    img_w: usize,
+    cap_total: usize,
+    dims: *const [3]usize,
+    lens: *const [3]usize,
+    theta: f32,
+) c_int;
+// The same tables written to device memory on the caller's stream.
+pub extern fn zdraw_cuda_klein_rope_table_device(
+    ctx: *anyopaque,
+    stream: ?*anyopaque,
+    cos_dev: [*]f32,
+    sin_dev: [*]f32,
+    txt_len: usize,
+    grid_h: usize,
+    grid_w: usize,
+    ref_h: usize,
+    ref_w: usize,
+    theta: f64,
+) c_int;
+pub extern fn zdraw_cuda_zimage_rope_table_device(
+    ctx: *anyopaque,
+    stream: ?*anyopaque,
+    cos_dev: [*]f32,
+    sin_dev: [*]f32,
+    img_h: usize,
+    img_w: usize,
+    cap_total: usize,
+    dims: *const [3]usize,
+    lens: *const [3]usize,
+    theta: f32,
+) c_int;
+
 pub const Error = error{ UnsupportedShape, InvalidShape, CudaFailed };
 
 pub fn check(code: c_int) Error!void {

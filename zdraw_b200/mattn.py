@@ -196,6 +196,35 @@ class Context:
                                                 _ptr(norm_w_txt), _ptr(norm_w_img), _ptr(rope_cos), _ptr(rope_sin),
                                                 C.byref(params)))
 
+    def klein_rope_table_device(self, txt_len: int, grid_h: int, grid_w: int, ref_h: int = 0, ref_w: int = 0,
+                                theta: float = 2000.0, stream=None):
+        """``buildRopeRef`` (src/klein/zflux2_dit.zig:125-170) on the GPU: cos, sin [tokens][128] f32 device tensors."""
+        import torch
+
+        tokens = txt_len + grid_h * grid_w + ref_h * ref_w
+        cos_t = torch.empty((tokens, HEAD_DIM), dtype=torch.float32, device=f"cuda:{self.device}")
+        sin_t = torch.empty_like(cos_t)
+        self._check(self._lib.zdraw_cuda_klein_rope_table_device(
+            self._h, self._stream_ptr(stream), _ptr(cos_t), _ptr(sin_t), txt_len, grid_h, grid_w, ref_h, ref_w,
+            float(theta)))
+        return cos_t, sin_t
+
+    def zimage_rope_table_device(self, img_h: int, img_w: int, cap_total: int, dims=(32, 48, 48),
+                                 lens=(1536, 512, 512), theta: float = 256.0, stream=None):
+        """``zrope.Cache`` gathered over [image | caption] (src/zimage/zrope.zig:32-116,
+        src/zimage/zunify.zig:16-37) on the GPU: cos, sin [tokens][128] f32 device tensors."""
+        import torch
+
+        tokens = img_h * img_w + cap_total
+        cos_t = torch.empty((tokens, HEAD_DIM), dtype=torch.float32, device=f"cuda:{self.device}")
+        sin_t = torch.empty_like(cos_t)
+        d = np.ascontiguousarray(dims, np.uintp)
+        ln = np.ascontiguousarray(lens, np.uintp)
+        self._check(self._lib.zdraw_cuda_zimage_rope_table_device(
+            self._h, self._stream_ptr(stream), _ptr(cos_t), _ptr(sin_t), img_h, img_w, cap_total, _ptr(d), _ptr(ln),
+            float(theta)))
+        return cos_t, sin_t
+
     def joint_attention_host(self, q, k, v, q_w_txt, q_w_img, k_w_txt, k_w_img, rope_cos, rope_sin, out,
                              params: AttnParams, key_mask=None) -> None:
         """The same with host buffers (numpy arrays or pinned torch CPU tensors); returns when ``out`` is filled."""
