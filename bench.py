@@ -347,13 +347,23 @@ def main():
             j = i % g_sets
             torch.matmul(acts[j], wts[j].t(), out=c_plain[j])
 
+        def gemm_qkv(i):  # q, k (prologue as epilogue) and v from one activation, one launch
+            j = i % g_sets
+            ctx.qkv_projection(acts[j], wts[j], wts[(j + 1) % g_sets], wts[(j + 2) % g_sets], c_qk[j],
+                               c_qk[(j + 1) % g_sets], c_plain[j], x0["q_w_txt"], x0["q_w_img"], x0["k_w_txt"],
+                               x0["k_w_img"], x0["rope_cos"], x0["rope_sin"], lp_qk, stream=stream)
+
         ms_gp, ms_gq, ms_gl = timed(gemm_plain), timed(gemm_qk), timed(gemm_library)
+        ms_g3 = timed(gemm_qkv) if g_sets >= 3 else None
         gemm_flops = 2.0 * m_rows * hidden * hidden
         projection = {
             "kernel": "linear_kernel", "m": m_rows, "n": hidden, "k": hidden, "bound": "tensor",
             "l2": f"operands rotate over {g_sets} sets ({g_sets * gemm_bytes / 1e6:.0f} MB)",
             "plain_f16": {"ms_per_launch": ms_gp, "achieved": gemm_flops / ms_gp / 1e9, "unit": "TFLOP/s"},
             "qk_epilogue": {"ms_per_launch": ms_gq, "achieved": gemm_flops / ms_gq / 1e9, "unit": "TFLOP/s"},
+            "qkv_one_launch": None if ms_g3 is None else {
+                "ms_per_launch": ms_g3, "achieved": 3 * gemm_flops / ms_g3 / 1e9, "unit": "TFLOP/s",
+                "note": "q and k with the prologue as epilogue + v plain, three weight matrices, one launch"},
             "cublas_f16": {"ms_per_launch": ms_gl, "achieved": gemm_flops / ms_gl / 1e9, "unit": "TFLOP/s",
                            "note": "torch.matmul on the same operands, no epilogue; for comparison only"},
         }
@@ -435,8 +445,9 @@ def main():
             "clocks": clocks,
         }
         if projection is not None:
-            for leg in ("plain_f16", "qk_epilogue", "cublas_f16"):
-                projection[leg]["frac"] = projection[leg]["achieved"] / peaks["bf16_tflops"]
+            for leg in ("plain_f16", "qk_epilogue", "qkv_one_launch", "cublas_f16"):
+                if projection[leg] is not None:
+                    projection[leg]["frac"] = projection[leg]["achieved"] / peaks["bf16_tflops"]
             projection["peak"] = peaks["bf16_tflops"]
             line["projection"] = projection
         if world == 1 and not args.no_cpu_baseline:

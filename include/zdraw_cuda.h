@@ -292,6 +292,21 @@ ZDRAW_CUDA_API int zdraw_cuda_linear(void *ctx, void *stream, const void *a, con
                                      const zdraw_cuda_linear_params *p);
 
 /*
+ * The three projections of one activation in one launch: q16 = prologue(x * wq^T),
+ * k16 = prologue(x * wk^T) (both fp16 head-major, as with epilogue 1 above) and v = x * wv^T
+ * (c_dtype, row-major with stride ld_c, i.e. the token-major V zdraw_cuda_attention reads with
+ * ld_v = ld_c). Replaces the three gemmRunF16A calls and the two rmsRopeHm that follow them in a
+ * double block (src/klein/zflux2_resident.zig:1473-1513, 1544-1558). p describes one product
+ * (m, n, k, strides; epilogue must be 1); wq, wk, wv are [n][ld_w] f16. One launch instead of
+ * three fills the GPU's tile waves better than three launches of 2.9 waves each.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_qkv_projection(void *ctx, void *stream, const void *x, const void *wq, const void *wk,
+                                             const void *wv, void *q16, void *k16, void *v, const float *q_w_txt,
+                                             const float *q_w_img, const float *k_w_txt, const float *k_w_img,
+                                             const float *rope_cos, const float *rope_sin,
+                                             const zdraw_cuda_linear_params *p);
+
+/*
  * Debugging aid, the counterpart of ZDRAW_KLEIN_TRACE's per-stage GPU times
  * (src/klein/zflux2_resident.zig:380-409): while a device buffer of at least 1600 64-bit words is
  * set, the first CTA of every attention launch writes clock stamps of its pipeline events

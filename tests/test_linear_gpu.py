@@ -139,3 +139,39 @@ def test_klein_projection_full_size_and_chain(ctx, oracle):
     assert dq <= 2 ** -8, f"fused epilogue q differs from projection + prologue by {dq}"
     d = (o_fused.float() - o_ref.float()).abs()
     assert d.max().item() <= 2e-3 and d.mean().item() <= 2e-4
+
+
+@pytest.mark.parametrize("batch,tokens,heads,txt,k,c_dtype", [(1, 4608, 24, 512, 3072, 1), (2, 300, 4, 100, 128, 3)])
+def test_qkv_projection_equals_three_separate_launches(ctx, batch, tokens, heads, txt, k, c_dtype):
+    """One launch over the three weight matrices gives the bytes of three zdraw_cuda_linear calls
+    (same tiles, same K order), with a padded V stride whose extra columns stay untouched."""
+    n, m = heads * 128, batch * tokens
+    gen = torch.Generator(device="cuda").manual_seed(tokens + k)
+    x = torch.randn((m, k), generator=gen, device="cuda").half()
+    wq, wk, wv = ((torch.randn((n, k), generator=gen, device="cuda") / k ** 0.5).half() for _ in range(3))
+    nw = [(torch.rand(128, generator=gen, device="cuda") * 0.4 + 0.8) for _ in range(4)]
+    cos_h, sin_h = mattn.klein_rope_table(txt, 1, tokens - txt)
+    cos_t, sin_t = torch.from_numpy(cos_h).cuda(), torch.from_numpy(sin_h).cuda()
+    ld_v = n + 64
+    vdt = torch.float16 if c_dtype == 1 else torch.float32
+    p = _lib.LinearParams(m=m, n=n, k=k, a_dtype=1, w_dtype=1, c_dtype=c_dtype, epilogue=1, ld_c=ld_v, tokens=tokens,
+                          heads=heads, txt_tokens=txt, norm_eps=1e-6)
+    q1 = torch.full((batch, heads, tokens, 128), float("nan"), dtype=torch.float16, device="cuda")
+    k1 = torch.full_like(q1, float("nan"))
+    v1 = torch.full((m, ld_v), float("nan"), dtype=vdt, device="cuda")
+    ctx.qkv_projection(x, wq, wk, wv, q1, k1, v1, nw[0], nw[1], nw[2], nw[3], cos_t, sin_t, p)
+    q3, k3, v3 = torch.empty_like(q1), torch.empty_like(k1), torch.full_like(v1, float("nan"))
+    p_qk = _lib.LinearParams(m=m, n=n, k=k, a_dtype=1, w_dtype=1, c_dtype=1, epilogue=1, tokens=tokens, heads=heads,
+                             txt_tokens=txt, norm_eps=1e-6)
+    p_v = _lib.LinearParams(m=m, n=n, k=k, a_dtype=1, w_dtype=1, c_dtype=c_dtype, epilogue=0, ld_c=ld_v)
+    ctx.linear(x, wq, q3, p_qk, nw[0], nw[1], cos_t, sin_t)
+    ctx.linear(x, wk, k3, p_qk, nw[2], nw[3], cos_t, sin_t)
+    ctx.linear(x, wv, v3, p_v)
+    torch.cuda.synchronize()
+    assert ctx.last_status() == 0
+    assert torch.equal(q1.view(torch.int16), q3.view(torch.int16))
+    assert torch.equal(k1.view(torch.int16), k3.view(torch.int16))
+    assert torch.equal(v1[:, :n], v3[:, :n]) and not torch.isnan(v1[:, :n].float()).any()
+    assert torch.isnan(v1[:, n:].float()).all()
+    with pytest.raises(mattn.InvalidShape):  # the grouped call is the q/k-prologue form only
+        ctx.qkv_projection(x, wq, wk, wv, q1, k1, v1, nw[0], nw[1], nw[2], nw[3], cos_t, sin_t, p_v)

@@ -618,16 +618,33 @@ int zdraw_cuda_last_status(void* ctx, void* stream, uint32_t* device_status) {
   return ZDRAW_CUDA_OK;
 }
 
-int zdraw_cuda_linear(void* ctx, void* stream, const void* a, const void* w, void* c, const float* norm_w_txt,
-                      const float* norm_w_img, const float* rope_cos, const float* rope_sin,
-                      const zdraw_cuda_linear_params* p) {
-  Ctx* cx = as_ctx(ctx);
-  if (!cx) return ZDRAW_CUDA_E_ARG;
+}  // extern "C"
+
+namespace {
+
+// One product of a projection launch as the entry points describe it.
+struct PartSpec {
+  const void* w;
+  void* c;
+  uint32_t epilogue;  // 0 plain, 1 qk
+  const float *w_txt, *w_img;
+};
+
+// Shared body of zdraw_cuda_linear and zdraw_cuda_qkv_projection: validates, builds the tensor
+// maps and launches one kernel that computes every part from the same A.
+int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec* parts, const float* rope_cos,
+               const float* rope_sin, const zdraw_cuda_linear_params* p) {
   if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
   if (p->reserved != 0 || p->m == 0 || p->n == 0 || p->k == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero size or reserved != 0");
-  if (p->epilogue > 1 || (p->c_dtype != ZDRAW_DTYPE_F16 && p->c_dtype != ZDRAW_DTYPE_F32))
-    return fail(cx, ZDRAW_CUDA_E_ARG, "bad epilogue or c_dtype");
-  if (!a || !w || !c || !aligned16(a) || !aligned16(w) || !aligned16(c)) return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned matrix");
+  if (p->c_dtype != ZDRAW_DTYPE_F16 && p->c_dtype != ZDRAW_DTYPE_F32) return fail(cx, ZDRAW_CUDA_E_ARG, "bad c_dtype");
+  if (!a || !aligned16(a)) return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned matrix");
+  bool any_qk = false;
+  for (int i = 0; i < n_parts; ++i) {
+    if (parts[i].epilogue > 1) return fail(cx, ZDRAW_CUDA_E_ARG, "bad epilogue");
+    if (!parts[i].w || !parts[i].c || !aligned16(parts[i].w) || !aligned16(parts[i].c))
+      return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned matrix");
+    any_qk = any_qk || parts[i].epilogue == 1;
+  }
   // Shapes and types outside the kernel: declined, nothing enqueued (the reference's fast GEMMs
   // admit 32-aligned dims only, src/metal/mres_util.zig:30-38).
   if (p->a_dtype != ZDRAW_DTYPE_F16 || p->w_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_DECLINED, "A and W must be f16");
@@ -642,46 +659,82 @@ int zdraw_cuda_linear(void* ctx, void* stream, const void* a, const void* w, voi
   la.m = static_cast<int>(p->m);
   la.n = static_cast<int>(p->n);
   la.k = static_cast<int>(p->k);
-  la.epilogue = static_cast<int>(p->epilogue);
-  la.c_f32 = p->c_dtype == ZDRAW_DTYPE_F32;
-  la.c = c;
-  la.ld_c = ld_c;
+  la.n_parts = n_parts;
   la.status = cx->d_status;
-  if (p->epilogue == 1) {
+  if (any_qk) {
     if (p->tokens == 0 || p->heads == 0 || p->m % p->tokens != 0 || p->n != p->heads * 128u || p->txt_tokens > p->tokens)
       return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs m = images * tokens and n = heads * 128");
-    if (p->c_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_E_ARG, "the qk epilogue writes f16");
-    if (!norm_w_txt || !norm_w_img || !rope_cos || !rope_sin || !aligned16(norm_w_txt) || !aligned16(norm_w_img) ||
-        !aligned16(rope_cos) || !aligned16(rope_sin) || p->rope_batch_stride % 4 != 0)
-      return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs aligned weights and tables");
+    if (!rope_cos || !rope_sin || !aligned16(rope_cos) || !aligned16(rope_sin) || p->rope_batch_stride % 4 != 0)
+      return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs aligned tables");
     if (!(p->norm_eps >= 0.0f)) return fail(cx, ZDRAW_CUDA_E_ARG, "norm_eps must be >= 0");
     la.tokens = static_cast<int>(p->tokens);
     la.heads = static_cast<int>(p->heads);
     la.txt_tokens = static_cast<int>(p->txt_tokens);
     la.norm_eps = p->norm_eps;
-    la.w_txt = norm_w_txt;
-    la.w_img = norm_w_img;
     la.rope_cos = rope_cos;
     la.rope_sin = rope_sin;
     la.rope_batch_stride = static_cast<long long>(p->rope_batch_stride);
   }
+  for (int i = 0; i < n_parts; ++i) {
+    zdraw::LinearPart& lp = la.part[i];
+    lp.epilogue = static_cast<int>(parts[i].epilogue);
+    lp.c = parts[i].c;
+    if (parts[i].epilogue == 1) {
+      if (!parts[i].w_txt || !parts[i].w_img || !aligned16(parts[i].w_txt) || !aligned16(parts[i].w_img))
+        return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs aligned norm weights");
+      lp.w_txt = parts[i].w_txt;
+      lp.w_img = parts[i].w_img;
+    } else {
+      lp.c_f32 = p->c_dtype == ZDRAW_DTYPE_F32;
+      lp.ld_c = ld_c;
+    }
+  }
   ZD_CUDA(cx, cudaSetDevice(cx->device));
   // Row-major f16 matrices [rows][ld] as tiled tensor maps: boxes of 64 columns x 128 rows.
-  CUtensorMap tm_a, tm_w;
+  zdraw::LinearMaps maps;
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  auto encode = [&](CUtensorMap* tm, const void* base_ptr, uint64_t rows, long long ld, uint32_t box_rows) {
+  auto encode = [&](CUtensorMap* tm, const void* base_ptr, uint64_t rows, long long ld) {
     const cuuint64_t dims[4] = {p->k, rows, 1, 1};
     const cuuint64_t strides[3] = {2ull * static_cast<cuuint64_t>(ld), 2ull * static_cast<cuuint64_t>(ld) * rows,
                                    2ull * static_cast<cuuint64_t>(ld) * rows};
-    const cuuint32_t box[4] = {64, box_rows, 1, 1};
+    const cuuint32_t box[4] = {64, 128, 1, 1};
     return cx->encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base_ptr), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
-  if (encode(&tm_a, a, p->m, ld_a, 128) != CUDA_SUCCESS || encode(&tm_w, w, p->n, ld_w, 128) != CUDA_SUCCESS)
-    return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
-  ZD_CUDA(cx, zdraw::launch_linear(static_cast<cudaStream_t>(stream), tm_a, tm_w, la, cx->sm_count));
+  if (encode(&maps.a, a, p->m, ld_a) != CUDA_SUCCESS) return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
+  for (int i = 0; i < zdraw::kMaxLinearParts; ++i)
+    if (encode(&maps.w[i], parts[i < n_parts ? i : 0].w, p->n, ld_w) != CUDA_SUCCESS)
+      return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
+  ZD_CUDA(cx, zdraw::launch_linear(static_cast<cudaStream_t>(stream), maps, la, cx->sm_count));
   return ZDRAW_CUDA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int zdraw_cuda_linear(void* ctx, void* stream, const void* a, const void* w, void* c, const float* norm_w_txt,
+                      const float* norm_w_img, const float* rope_cos, const float* rope_sin,
+                      const zdraw_cuda_linear_params* p) {
+  Ctx* cx = as_ctx(ctx);
+  if (!cx) return ZDRAW_CUDA_E_ARG;
+  if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
+  if (p->epilogue == 1 && p->c_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_E_ARG, "the qk epilogue writes f16");
+  const PartSpec part = {w, c, p->epilogue, norm_w_txt, norm_w_img};
+  return run_linear(cx, stream, a, 1, &part, rope_cos, rope_sin, p);
+}
+
+int zdraw_cuda_qkv_projection(void* ctx, void* stream, const void* x, const void* wq, const void* wk, const void* wv,
+                              void* q16, void* k16, void* v, const float* q_w_txt, const float* q_w_img,
+                              const float* k_w_txt, const float* k_w_img, const float* rope_cos,
+                              const float* rope_sin, const zdraw_cuda_linear_params* p) {
+  Ctx* cx = as_ctx(ctx);
+  if (!cx) return ZDRAW_CUDA_E_ARG;
+  if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
+  if (p->epilogue != 1) return fail(cx, ZDRAW_CUDA_E_ARG, "the q/k/v projection takes epilogue = 1 (q and k get the prologue)");
+  const PartSpec parts[3] = {{wq, q16, 1, q_w_txt, q_w_img}, {wk, k16, 1, k_w_txt, k_w_img}, {wv, v, 0, nullptr, nullptr}};
+  return run_linear(cx, stream, x, 3, parts, rope_cos, rope_sin, p);
 }
 
 int zdraw_cuda_attn_set_trace(void* ctx, void* device_words, size_t n_words) {

@@ -86,8 +86,7 @@ __device__ __forceinline__ uint32_t pack_clamped(float lo, float hi) {
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-              const LinearArgs a) {
+linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t base = smem_u32(smem_raw);
   volatile uint32_t* flags = reinterpret_cast<volatile uint32_t*>(smem_raw + kOffFlags);
@@ -98,9 +97,9 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();  // 0: issues the pair's MMAs
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int tiles_n = a.n / kTN;
+  const int tiles_n = a.n / kTN;                        // column blocks of one part
   const int tiles_m = (a.m + 2 * kTM - 1) / (2 * kTM);  // pair tiles: 256 rows
-  const int n_tiles = tiles_m * tiles_n;
+  const int n_tiles = tiles_m * tiles_n * a.n_parts;
   const int k_steps = a.k / kTK;
 
   if (threadIdx.x == 0) {
@@ -140,13 +139,15 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      tma_prefetch_desc(&tm_a);
-      tma_prefetch_desc(&tm_w);
+      tma_prefetch_desc(&maps.a);
+      for (int pt = 0; pt < a.n_parts; ++pt) tma_prefetch_desc(&maps.w[pt]);
       uint32_t it = 0;
       bool ok = *abort_flag == 0u;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-        // Consecutive tiles share the W block (tile_n) and walk down the rows: W stays in L2.
-        const int tile_n = tile / tiles_m, tile_m = tile % tiles_m;
+        // Consecutive tiles share the W block (part, tile_n) and walk down the rows: W stays in L2.
+        const int col = tile / tiles_m, tile_m = tile % tiles_m;
+        const int tile_n = col % tiles_n;
+        const CUtensorMap* tm_w = &maps.w[col / tiles_n];
         const int row_a = (2 * tile_m + static_cast<int>(rank)) * kTM;
         const int row_w = tile_n * kTN + static_cast<int>(rank) * (kTN / 2);
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
@@ -158,8 +159,8 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
           // Both CTAs' bytes are counted on the even CTA's barrier, which expects all of them.
           const uint32_t full = cluster_map(bar(kBarFull + stage), 0);
           if (rank == 0) mbar_arrive_expect_tx(bar(kBarFull + stage), 2 * kStageBytes);
-          tma_load_4d_pair(dst, &tm_a, full, ks * kTK, row_a, 0, 0);
-          tma_load_4d_pair(dst + kABytes, &tm_w, full, ks * kTK, row_w, 0, 0);
+          tma_load_4d_pair(dst, &maps.a, full, ks * kTK, row_a, 0, 0);
+          tma_load_4d_pair(dst + kABytes, tm_w, full, ks * kTK, row_w, 0, 0);
         }
       }
       if (!ok) {
@@ -215,7 +216,9 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
     int local = 0;
     bool ok = __all_sync(0xffffffffu, *abort_flag == 0u);  // warp-uniform
     for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
-      const int tile_n = tile / tiles_m, tile_m = 2 * (tile % tiles_m) + static_cast<int>(rank);
+      const int col = tile / tiles_m, tile_m = 2 * (tile % tiles_m) + static_cast<int>(rank);
+      const int tile_n = col % tiles_n;
+      const LinearPart& part = a.part[col / tiles_n];
       const int b = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
       ok = __all_sync(0xffffffffu, wait_bar(bar(kBarAccFull + b), use & 1u, abort_flag, a.status));
@@ -225,22 +228,22 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
       const long long m = static_cast<long long>(tile_m) * kTM + row;
       const bool live = m < a.m;
 
-      if (a.epilogue == kEpiloguePlain) {
+      if (part.epilogue == kEpiloguePlain) {
 #pragma unroll 1
         for (int ch = 4 * hh; ch < 4 * hh + 4; ++ch) {
           uint32_t x[32];
           tmem_ld_x32(t_acc + 32u * ch, x);
           tmem_wait_ld();
           if (live) {
-            const long long off = m * a.ld_c + static_cast<long long>(tile_n) * kTN + 32 * ch;
-            if (a.c_f32) {
-              float4* dst = reinterpret_cast<float4*>(static_cast<float*>(a.c) + off);
+            const long long off = m * part.ld_c + static_cast<long long>(tile_n) * kTN + 32 * ch;
+            if (part.c_f32) {
+              float4* dst = reinterpret_cast<float4*>(static_cast<float*>(part.c) + off);
 #pragma unroll
               for (int i = 0; i < 8; ++i)
                 dst[i] = make_float4(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1]),
                                      __uint_as_float(x[4 * i + 2]), __uint_as_float(x[4 * i + 3]));
             } else {
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(a.c) + off);
+              uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(part.c) + off);
 #pragma unroll
               for (int i = 0; i < 4; ++i)
                 dst[i] = make_uint4(pack_clamped(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
@@ -255,7 +258,7 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
         const long long mm = live ? m : 0;
         const int tok = static_cast<int>(mm % a.tokens);
         const int img = static_cast<int>(mm / a.tokens);
-        const float* w = (tok < a.txt_tokens) ? a.w_txt : a.w_img;
+        const float* w = (tok < a.txt_tokens) ? part.w_txt : part.w_img;
         // Offsets into the cos/sin tables of the rows this lane fetches for the warp (see pass 2).
         const long long my_off = static_cast<long long>(img) * a.rope_batch_stride + static_cast<long long>(tok) * 128;
         long long roff[4];
@@ -286,7 +289,7 @@ linear_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ 
           // so the warp fetches 8 rows x 64 bytes per load instruction (lane -> row lane/4,
           // 16-byte piece lane%4), parks them in shared memory and each thread reads its own row
           // back. The next 16 columns are in flight while these are rotated.
-          __half* dst = static_cast<__half*>(a.c) +
+          __half* dst = static_cast<__half*>(part.c) +
                         ((static_cast<long long>(img) * a.heads + head) * a.tokens + tok) * 128;
           float4 pc[4], ps[4];
 #pragma unroll
@@ -359,9 +362,8 @@ cudaError_t linear_configure() {
   return cudaFuncSetAttribute(linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
-cudaError_t launch_linear(cudaStream_t stream, const CUtensorMap& tm_a, const CUtensorMap& tm_w,
-                          const LinearArgs& args, int sm_count) {
-  const int n_tiles = ((args.m + 2 * kTM - 1) / (2 * kTM)) * (args.n / kTN);
+cudaError_t launch_linear(cudaStream_t stream, const LinearMaps& maps, const LinearArgs& args, int sm_count) {
+  const int n_tiles = ((args.m + 2 * kTM - 1) / (2 * kTM)) * (args.n / kTN) * args.n_parts;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
@@ -391,7 +393,7 @@ cudaError_t launch_linear(cudaStream_t stream, const CUtensorMap& tm_a, const CU
     if (device >= 0 && device < 64) pairs_of_device[device] = pairs;
   }
   cfg.gridDim = dim3(2 * (n_tiles < pairs ? n_tiles : pairs));
-  return cudaLaunchKernelEx(&cfg, linear_kernel, tm_a, tm_w, args);
+  return cudaLaunchKernelEx(&cfg, linear_kernel, maps, args);
 }
 
 }  // namespace zdraw

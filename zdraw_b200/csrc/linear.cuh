@@ -10,25 +10,38 @@ namespace zdraw {
 constexpr int kEpiloguePlain = 0;
 constexpr int kEpilogueQk = 1;
 
-// C[m, n] = A[m, k] * W[n, k]^T. A and W are reached through tensor maps (f16, 128-byte swizzle,
-// boxes of 64 columns x 128 rows). n % 256 == 0, k % 64 == 0.
-struct LinearArgs {
-  int m, n, k;
+constexpr int kMaxLinearParts = 3;
+
+// One output of a launch: C_p[m, n] = A[m, k] * W_p[n, k]^T with its own epilogue.
+struct LinearPart {
   int epilogue;  // kEpiloguePlain | kEpilogueQk
   int c_f32;     // plain: 1 = f32 C, 0 = f16 C
   void* c;       // plain: [m][ld_c]; qk: f16 head-major [image][head][token][128]
   long long ld_c;
+  const float *w_txt, *w_img;  // qk: norm weights [128]
+};
+
+// Up to three products that share A (the Q, K and V projections of one activation) run as one
+// launch over n_parts * (n / 256) column blocks. A and every W are reached through tensor maps
+// (f16, 128-byte swizzle, boxes of 64 columns x 128 rows). n % 256 == 0, k % 64 == 0.
+struct LinearArgs {
+  int m, n, k;
+  int n_parts;
+  LinearPart part[kMaxLinearParts];
   // qk epilogue (n == heads * 128, m == images * tokens)
   int tokens, heads, txt_tokens;
   float norm_eps;
-  const float *w_txt, *w_img;        // [128]
   const float *rope_cos, *rope_sin;  // [tokens][128]
   long long rope_batch_stride;
   uint32_t* status;
 };
 
+struct LinearMaps {
+  CUtensorMap a;
+  CUtensorMap w[kMaxLinearParts];  // unused entries repeat w[0]
+};
+
 cudaError_t linear_configure();
-cudaError_t launch_linear(cudaStream_t stream, const CUtensorMap& tm_a, const CUtensorMap& tm_w,
-                          const LinearArgs& args, int sm_count);
+cudaError_t launch_linear(cudaStream_t stream, const LinearMaps& maps, const LinearArgs& args, int sm_count);
 
 }  // namespace zdraw

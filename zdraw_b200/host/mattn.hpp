@@ -121,6 +121,16 @@ class Context {
     return from_code(zdraw_cuda_linear(ctx_, stream, a, w, c, norm_w_txt, norm_w_img, rope_cos, rope_sin, &p));
   }
 
+  // Three gemmRunF16A + two rmsRopeHm of a double block (src/klein/zflux2_resident.zig:1473-1513,
+  // 1544-1558) in one launch.
+  Error qkv_projection(void* stream, const void* x, const void* wq, const void* wk, const void* wv, void* q16,
+                       void* k16, void* v, const float* q_w_txt, const float* q_w_img, const float* k_w_txt,
+                       const float* k_w_img, const float* rope_cos, const float* rope_sin,
+                       const zdraw_cuda_linear_params& p) {
+    return from_code(zdraw_cuda_qkv_projection(ctx_, stream, x, wq, wk, wv, q16, k16, v, q_w_txt, q_w_img, k_w_txt,
+                                               k_w_img, rope_cos, rope_sin, &p));
+  }
+
   uint32_t last_status(void* stream = nullptr) {
     uint32_t st = 0;
     zdraw_cuda_last_status(ctx_, stream, &st);

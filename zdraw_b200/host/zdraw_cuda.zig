@@ -120,6 +120,24 @@ pub extern fn zdraw_cuda_linear(
     rope_sin: ?[*]const f32,
     params: *const LinearParams,
 ) c_int;
+pub extern fn zdraw_cuda_qkv_projection(
+    ctx: *anyopaque,
+    stream: ?*anyopaque,
+    x_f16: *const anyopaque,
+    wq_f16: *const anyopaque,
+    wk_f16: *const anyopaque,
+    wv_f16: *const anyopaque,
+    q16_hm: *anyopaque,
+    k16_hm: *anyopaque,
+    v: *anyopaque,
+    q_w_txt: [*]const f32,
+    q_w_img: [*]const f32,
+    k_w_txt: [*]const f32,
+    k_w_img: [*]const f32,
+    rope_cos: [*]const f32,
+    rope_sin: [*]const f32,
+    params: *const LinearParams,
+) c_int;
 pub extern fn zdraw_cuda_attention_host(
     ctx: *anyopaque,
     q: *const anyopaque,

@@ -196,6 +196,16 @@ class Context:
                                                 _ptr(norm_w_txt), _ptr(norm_w_img), _ptr(rope_cos), _ptr(rope_sin),
                                                 C.byref(params)))
 
+    def qkv_projection(self, x, wq, wk, wv, q16, k16, v, q_w_txt, q_w_img, k_w_txt, k_w_img, rope_cos, rope_sin,
+                       params: LinearParams, stream=None) -> None:
+        """The three ``gemmRunF16A`` calls and two ``rmsRopeHm`` of a double block
+        (src/klein/zflux2_resident.zig:1473-1513, 1544-1558) as one launch: q16, k16 fp16 head-major,
+        v token-major."""
+        self._check(self._lib.zdraw_cuda_qkv_projection(
+            self._h, self._stream_ptr(stream), _ptr(x), _ptr(wq), _ptr(wk), _ptr(wv), _ptr(q16), _ptr(k16), _ptr(v),
+            _ptr(q_w_txt), _ptr(q_w_img), _ptr(k_w_txt), _ptr(k_w_img), _ptr(rope_cos), _ptr(rope_sin),
+            C.byref(params)))
+
     def klein_rope_table_device(self, txt_len: int, grid_h: int, grid_w: int, ref_h: int = 0, ref_w: int = 0,
                                 theta: float = 2000.0, stream=None):
         """``buildRopeRef`` (src/klein/zflux2_dit.zig:125-170) on the GPU: cos, sin [tokens][128] f32 device tensors."""
