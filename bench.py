@@ -371,6 +371,28 @@ def main():
         if ctx.last_status() != 0:
             raise SystemExit("the projection kernel reported a non-zero status")
 
+    # ---- the other attention shape next to the path: one head of 512 channels over 16384 tokens
+    #      (VAE mid-block at 1024 px), built from the projection kernel and a row softmax
+    wide = None
+    if not by_heads:
+        wt, wd = 16384, 512
+        g = torch.Generator(device="cuda").manual_seed(w.seed + 11)
+        wq, wk, wv = (torch.randn((wt, wd), device="cuda", generator=g) for _ in range(3))
+        wo = torch.empty((wt, wd), device="cuda")
+        wcfg = mattn.Config(wt, 1, 1, wd)
+
+        def wide_step(i):
+            ctx.wide_attention(wq, wk, wv, wo, wcfg, stream=stream)
+
+        ms_w = timed(wide_step)
+        wide = {"api": "zdraw_cuda_wide_attention", "tokens": wt, "head_dim": wd, "ms_per_call": ms_w,
+                "achieved": 4.0 * wt * wt * wd / ms_w / 1e9, "unit": "TFLOP/s",
+                "kernels": "2 casts, transpose, linear_kernel (S), row_softmax_kernel, linear_kernel (O)",
+                "l2": "scores and probabilities (1.6 GB) stream through HBM"}
+        del wq, wk, wv, wo
+        if ctx.last_status() != 0:
+            raise SystemExit("the wide attention reported a non-zero status")
+
     # ---- end to end from pinned host buffers through the host-buffer C-ABI entry point
     xh = workloads.make_inputs(w, "cpu", pin=True)
     p_host = workloads.params(w, heads=hs.count, out_layout=1 if by_heads else 0)
@@ -450,6 +472,9 @@ def main():
                     projection[leg]["frac"] = projection[leg]["achieved"] / peaks["bf16_tflops"]
             projection["peak"] = peaks["bf16_tflops"]
             line["projection"] = projection
+        if wide is not None:
+            wide["frac"] = wide["achieved"] / peaks["bf16_tflops"]
+            line["wide_attention"] = wide
         if world == 1 and not args.no_cpu_baseline:
             import oracle
 

@@ -1,0 +1,93 @@
+"""Wide-head attention (one head, head_dim 512: the VAE mid-block shape, src/metal/mvattn_owned.zig)
+against the oracle's CPU attention (src/runtime/attention.zig:21-98) through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from zdraw_b200 import mattn
+
+pytestmark = pytest.mark.gpu
+
+# fp16 operands with f32 accumulation and half probabilities against the f32 oracle, N(0,1) inputs:
+# the bounds the attention tests use for fp16 I/O.
+MAX_ABS, MEAN_ABS = 1e-2, 1e-3
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = mattn.Context(0)
+    yield c
+    c.deinit()
+
+
+def make(tokens, dim, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return tuple(torch.randn((tokens, dim), generator=g, device="cuda") * scale for _ in range(3))
+
+
+@pytest.mark.parametrize("tokens,dim", [(256, 256), (768, 512), (1024, 512)])
+def test_small_shapes_match_cpu_attention(ctx, oracle, tokens, dim):
+    q, k, v = make(tokens, dim, tokens + dim)
+    out = torch.full((tokens, dim), float("nan"), device="cuda")
+    ctx.wide_attention(q, k, v, out, mattn.Config(tokens, 1, 1, dim))
+    torch.cuda.synchronize()
+    assert ctx.last_status() == 0
+    want = oracle.sdpa(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), heads=1)
+    err = np.abs(out.cpu().numpy() - want.reshape(tokens, dim))
+    assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS
+
+
+def test_vae_mid_block_shape_sampled_rows_and_repeat(ctx, oracle):
+    """16384 tokens x 512 channels (1024 px): sampled query rows against the oracle, every output
+    element written, and a second run bit-identical."""
+    tokens, dim = 16384, 512
+    q, k, v = make(tokens, dim, 7)
+    out = torch.full((tokens, dim), float("nan"), device="cuda")
+    cfg = mattn.Config(tokens, 1, 1, dim)
+    ctx.wide_attention(q, k, v, out, cfg)
+    again = torch.empty_like(out)
+    ctx.wide_attention(q, k, v, again, cfg)
+    torch.cuda.synchronize()
+    assert ctx.last_status() == 0
+    assert torch.equal(out, again)
+    assert torch.isfinite(out).all()
+    qh, kh, vh = q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy()
+    got = out.cpu().numpy()
+    for r in (0, 255, 256, 8191, 16383):
+        want = oracle.sdpa(qh, kh, vh, heads=1, rows=(r, r + 1)).reshape(tokens, dim)[r]
+        err = np.abs(got[r] - want)
+        assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS, f"row {r}: {err.max()}"
+
+
+def test_constant_values_and_peaked_scores(ctx):
+    """Properties that need no oracle: constant V rows come back as that constant; a query that
+    matches one key far better than the rest returns that key's value."""
+    tokens, dim = 512, 512
+    q, k, _ = make(tokens, dim, 3)
+    v = torch.full((tokens, dim), 0.75, device="cuda")
+    out = torch.empty((tokens, dim), device="cuda")
+    ctx.wide_attention(q, k, v, out, mattn.Config(tokens, 1, 1, dim))
+    assert torch.allclose(out, v, atol=2e-3)
+    k2 = torch.randn((tokens, dim), device="cuda") * 0.01
+    q2 = torch.zeros((tokens, dim), device="cuda")
+    k2[5] = 1.0
+    q2[:] = 4.0  # score with key 5 = 4 * 512 / sqrt(512) = 90 above the rest
+    v2 = torch.randn((tokens, dim), device="cuda")
+    ctx.wide_attention(q2, k2, v2, out, mattn.Config(tokens, 1, 1, dim))
+    torch.cuda.synchronize()
+    assert torch.allclose(out, v2[5].half().float().expand_as(out), atol=2e-3)
+
+
+def test_shapes_outside_the_kernels_are_declined(ctx):
+    x = torch.zeros((288, 512), device="cuda")
+    o = torch.empty_like(x)
+    with pytest.raises(mattn.UnsupportedShape):
+        ctx.wide_attention(x, x, x, o, mattn.Config(288, 1, 1, 512))  # tokens % 256 != 0
+    y = torch.zeros((256, 128), device="cuda")
+    with pytest.raises(mattn.UnsupportedShape):
+        ctx.wide_attention(y, y, y, torch.empty_like(y), mattn.Config(256, 1, 1, 128))  # head_dim % 256 != 0
+    with pytest.raises(mattn.UnsupportedShape):
+        ctx.wide_attention(x, x, x, o, mattn.Config(256, 2, 2, 512))  # more than one head
+    with pytest.raises(mattn.UnsupportedShape):
+        ctx.wide_attention(x, x, x, o, mattn.Config(256, 1, 1, 512, causal=True))
+    assert ctx.last_status() == 0

@@ -82,6 +82,7 @@ SYMBOLS = {
     "zdraw_cuda_last_status": (C.c_int, [_VP, _VP, C.POINTER(C.c_uint32)]),
     "zdraw_cuda_linear": (C.c_int, [_VP] * 9 + [C.POINTER(LinearParams)]),
     "zdraw_cuda_qkv_projection": (C.c_int, [_VP] * 15 + [C.POINTER(LinearParams)]),
+    "zdraw_cuda_wide_attention": (C.c_int, [_VP] * 6 + [C.c_size_t, C.c_size_t]),
     "zdraw_cuda_attn_set_trace": (C.c_int, [_VP, _VP, C.c_size_t]),
     "zdraw_cuda_last_error": (C.c_char_p, [_VP]),
 }

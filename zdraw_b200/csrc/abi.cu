@@ -15,6 +15,7 @@
 #include "attention_fwd.cuh"
 #include "linear.cuh"
 #include "rope_table.cuh"
+#include "wide_attention.cuh"
 #include "prologue.cuh"
 
 namespace {
@@ -53,6 +54,7 @@ struct Ctx {
   // Grow-only scratch (device memory).
   Buf q16, k16, v16, tile_list;
   Buf st_q, st_k, st_v, st_o, st_w, st_cos, st_sin, st_mask;  // staging for the host-buffer path
+  Buf wa_q16, wa_k16, wa_vt16, wa_s, wa_p;                     // wide-head attention: half operands, scores, probabilities
   char err[256] = {0};
 };
 
@@ -382,7 +384,8 @@ int zdraw_cuda_attn_destroy(void* ctx) {
   cudaSetDevice(c->device);
   cudaDeviceSynchronize();
   Buf* bufs[] = {&c->q16, &c->k16, &c->v16, &c->tile_list, &c->st_q, &c->st_k, &c->st_v,
-                 &c->st_o, &c->st_w, &c->st_cos, &c->st_sin, &c->st_mask};
+                 &c->st_o, &c->st_w, &c->st_cos, &c->st_sin, &c->st_mask,
+                 &c->wa_q16, &c->wa_k16, &c->wa_vt16, &c->wa_s, &c->wa_p};
   for (Buf* b : bufs)
     if (b->p) cudaFree(b->p);
   if (c->d_status) cudaFree(c->d_status);
@@ -723,6 +726,54 @@ int zdraw_cuda_linear(void* ctx, void* stream, const void* a, const void* w, voi
   if (p->epilogue == 1 && p->c_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_E_ARG, "the qk epilogue writes f16");
   const PartSpec part = {w, c, p->epilogue, norm_w_txt, norm_w_img};
   return run_linear(cx, stream, a, 1, &part, rope_cos, rope_sin, p);
+}
+
+int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const float* k, const float* v, float* o,
+                              size_t tokens, size_t head_dim) {
+  Ctx* cx = as_ctx(ctx);
+  if (!cx) return ZDRAW_CUDA_E_ARG;
+  if (!q || !k || !v || !o || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
+    return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned tensor");
+  if (tokens == 0 || head_dim == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero tokens or head_dim");
+  // Shapes outside the kernels are declined (the reference's own admission is tokens % 32 and
+  // head_dim % 32, src/metal/mvattn_owned.zig:271-272): both products run on the 256-column tiles
+  // of the projection kernel and a score row must fit one softmax block.
+  if (tokens % 256 != 0 || head_dim % 256 != 0 || tokens > 32768 || head_dim > 4096)
+    return fail(cx, ZDRAW_CUDA_DECLINED, "tokens and head_dim must be multiples of 256, tokens <= 32768");
+  ZD_CUDA(cx, cudaSetDevice(cx->device));
+  const size_t n = tokens * head_dim;
+  int rc;
+  if ((rc = ensure(cx, cx->wa_q16, n * 2)) || (rc = ensure(cx, cx->wa_k16, n * 2)) || (rc = ensure(cx, cx->wa_vt16, n * 2)) ||
+      (rc = ensure(cx, cx->wa_s, tokens * tokens * 4)) || (rc = ensure(cx, cx->wa_p, tokens * tokens * 2)))
+    return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // kf32_to_h x2, kvt_transpose_h (mvattn_owned.zig:322-330)
+  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16(st, q, cx->wa_q16.p, static_cast<long long>(tokens), static_cast<int>(head_dim),
+                                            static_cast<long long>(head_dim)));
+  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16(st, k, cx->wa_k16.p, static_cast<long long>(tokens), static_cast<int>(head_dim),
+                                            static_cast<long long>(head_dim)));
+  ZD_CUDA(cx, zdraw::launch_transpose_cast(st, v, cx->wa_vt16.p, static_cast<int>(tokens), static_cast<int>(head_dim)));
+  // S[tokens, tokens] = Q K^T (K is already [n][k]), f32 out
+  zdraw_cuda_linear_params ps = {};
+  ps.m = static_cast<uint32_t>(tokens);
+  ps.n = static_cast<uint32_t>(tokens);
+  ps.k = static_cast<uint32_t>(head_dim);
+  ps.a_dtype = ps.w_dtype = ZDRAW_DTYPE_F16;
+  ps.c_dtype = ZDRAW_DTYPE_F32;
+  const PartSpec part_s = {cx->wa_k16.p, cx->wa_s.p, 0, nullptr, nullptr};
+  if ((rc = run_linear(cx, stream, cx->wa_q16.p, 1, &part_s, nullptr, nullptr, &ps)) != 0) return rc;
+  // P = softmax(S / sqrt(head_dim)) in half
+  ZD_CUDA(cx, zdraw::launch_row_softmax(st, static_cast<const float*>(cx->wa_s.p), cx->wa_p.p, static_cast<long long>(tokens),
+                                        static_cast<int>(tokens), 1.0f / std::sqrt(static_cast<float>(head_dim))));
+  // O[tokens, head_dim] = P (V^T)^T, f32 out
+  zdraw_cuda_linear_params po = {};
+  po.m = static_cast<uint32_t>(tokens);
+  po.n = static_cast<uint32_t>(head_dim);
+  po.k = static_cast<uint32_t>(tokens);
+  po.a_dtype = po.w_dtype = ZDRAW_DTYPE_F16;
+  po.c_dtype = ZDRAW_DTYPE_F32;
+  const PartSpec part_o = {cx->wa_vt16.p, o, 0, nullptr, nullptr};
+  return run_linear(cx, stream, cx->wa_p.p, 1, &part_o, nullptr, nullptr, &po);
 }
 
 int zdraw_cuda_qkv_projection(void* ctx, void* stream, const void* x, const void* wq, const void* wk, const void* wv,

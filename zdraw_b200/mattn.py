@@ -206,6 +206,14 @@ class Context:
             _ptr(q_w_txt), _ptr(q_w_img), _ptr(k_w_txt), _ptr(k_w_img), _ptr(rope_cos), _ptr(rope_sin),
             C.byref(params)))
 
+    def wide_attention(self, q, k, v, out, cfg: Config, stream=None) -> None:
+        """``mvattn_owned.run`` (src/metal/mvattn_owned.zig:259-330): one head of head_dim 512 over device
+        tensors [tokens, head_dim] f32 (the VAE mid-block attention)."""
+        if cfg.heads != 1 or cfg.kv_heads != 1 or cfg.causal:
+            raise UnsupportedShape("wide attention is one head, non-causal")
+        self._check(self._lib.zdraw_cuda_wide_attention(self._h, self._stream_ptr(stream), _ptr(q), _ptr(k), _ptr(v),
+                                                        _ptr(out), cfg.tokens, cfg.head_dim))
+
     def klein_rope_table_device(self, txt_len: int, grid_h: int, grid_w: int, ref_h: int = 0, ref_w: int = 0,
                                 theta: float = 2000.0, stream=None):
         """``buildRopeRef`` (src/klein/zflux2_dit.zig:125-170) on the GPU: cos, sin [tokens][128] f32 device tensors."""

@@ -20,9 +20,10 @@ def main() -> None:
     ap.add_argument("--workload", default="klein_1024", choices=sorted(workloads.WORKLOADS))
     ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch")
-    ap.add_argument("--case", default="joint", choices=["joint", "linear_plain", "linear_qk"],
+    ap.add_argument("--case", default="joint", choices=["joint", "linear_plain", "linear_qk", "wide"],
                     help="joint: prologue + attention; linear_*: one projection GEMM (linear_kernel) of the "
-                         "workload's token count and hidden size, plain f16 store or fused q/k epilogue")
+                         "workload's token count and hidden size, plain f16 store or fused q/k epilogue; "
+                         "wide: one-head attention, 16384 tokens x 512 channels (ignores --workload)")
     args = ap.parse_args()
     w = workloads.WORKLOADS[args.workload]
     if args.batch:
@@ -37,7 +38,7 @@ def main() -> None:
                             x["rope_cos"], x["rope_sin"], out, p, key_mask=x["key_mask"])
 
     flops = w.flops
-    if args.case != "joint":
+    if args.case in ("linear_plain", "linear_qk"):
         from ._lib import LinearParams
 
         m, hidden = w.batch * w.tokens, w.heads * 128
@@ -58,6 +59,15 @@ def main() -> None:
 
             def call():
                 ctx.linear(a, wt, c, lp, x["q_w_txt"], x["q_w_img"], x["rope_cos"], x["rope_sin"])
+
+    if args.case == "wide":
+        wt, wd = 16384, 512
+        wq, wk, wv = (torch.randn((wt, wd), device="cuda") for _ in range(3))
+        wo = torch.empty((wt, wd), device="cuda")
+        flops = 4.0 * wt * wt * wd
+
+        def call():
+            ctx.wide_attention(wq, wk, wv, wo, mattn.Config(wt, 1, 1, wd))
 
     call()  # first call sizes the context scratch
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
