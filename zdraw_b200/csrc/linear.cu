@@ -12,7 +12,7 @@
 //
 // Persistent, warp-specialised, one CTA pair (cluster of two, tcgen05 cta_group::2) per 256 x 256
 // tile of C: each CTA stages its own 128 rows of A and 128 of the tile's 256 rows of W
-// (128B-swizzled 64-wide K slices, 32 KB per stage, 6 stages, TMA without multicast), the
+// (128B-swizzled 64-wide K slices, 32 KB per stage, 5 stages, TMA without multicast), the
 // even-rank CTA's warp 1 issues M256 N256 K16 MMAs that read A from each CTA's own shared memory
 // and W from both, and each CTA ends up with its 128 rows x 256 columns of the accumulator in
 // its own TMEM. Pairing halves the bytes each SM pulls from L2 per MMA compared with a lone CTA
@@ -36,7 +36,7 @@ namespace {
 constexpr int kTM = 128;                 // rows of C per CTA (256 per pair)
 constexpr int kTN = 256;                 // columns of C per tile (two heads of 128)
 constexpr int kTK = 64;                  // K per stage: one 128-byte swizzled row of f16
-constexpr int kStages = 6;
+constexpr int kStages = 5;
 constexpr int kABytes = kTM * kTK * 2;        // 16 KB: this CTA's rows of A
 constexpr int kBBytes = (kTN / 2) * kTK * 2;  // 16 KB: this CTA's half of the tile's rows of W
 constexpr int kStageBytes = kABytes + kBBytes;
@@ -52,9 +52,12 @@ constexpr int kBarAccEmpty = 2 * kStages + 2;  // [2] even CTA only: both CTAs' 
 constexpr int kBarDrain = 2 * kStages + 4;     // [1]
 constexpr int kNumBars = 2 * kStages + 5;
 constexpr int kOffFlags = kOffBar + kNumBars * 8;
-// qk epilogue: per epilogue warp, 16 columns of 32 tokens' cos and sin rows (2 x 32 x 64 bytes).
-constexpr int kTabBytesPerWarp = 2 * 32 * 64;
-constexpr int kOffTab = (kOffFlags + 16 + 127) / 128 * 128;
+// Per epilogue warp 8 KB: qk epilogue, 16 columns of 32 tokens' cos and sin rows (2 x 32 x 64
+// bytes, the first half); plain epilogue, four 2 KB blocks of 64-byte row pieces on their way
+// to a tile store (a store takes over a thousand clocks to read its block, so several must be
+// in flight per warp to drain a 128 x 256 f32 tile in the time the next tile's MMAs take).
+constexpr int kTabBytesPerWarp = 8192;
+constexpr int kOffTab = (kOffFlags + 16 + 1023) / 1024 * 1024;  // swizzled blocks: 1024-byte aligned
 constexpr int kSmemBytes = kOffTab + 8 * kTabBytesPerWarp;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
@@ -229,28 +232,54 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
       const bool live = m < a.m;
 
       if (part.epilogue == kEpiloguePlain) {
+        // A thread holds consecutive columns of ITS row, and rows lie ld_c apart, so storing from
+        // registers would touch 32 different lines per instruction. Instead the warp parks its
+        // 32 rows x 32 columns in shared memory in the tensor map's swizzle (128-byte rows of f32,
+        // 64-byte rows of f16) and one lane hands the block to TMA, which writes it as a tile (rows past m
+        // are clipped by the tensor map). The blocks rotate, so the next piece is read from TMEM while
+        // the previous ones are on their way out.
+        const CUtensorMap* tm_c = &maps.c[col / tiles_n];
+        uint4* stage = reinterpret_cast<uint4*>(smem_raw + kOffTab + (warp - 4) * kTabBytesPerWarp);
+        const uint32_t stage_addr = base + kOffTab + (warp - 4) * kTabBytesPerWarp;
+        const int row0 = tile_m * kTM + quarter * 32;  // first row of this warp
+        const int col_base = tile_n * kTN + 128 * hh;
 #pragma unroll 1
-        for (int ch = 4 * hh; ch < 4 * hh + 4; ++ch) {
+        for (int pc = 0; pc < 4; ++pc) {  // 32 columns of this warp's 128 at a time
           uint32_t x[32];
-          tmem_ld_x32(t_acc + 32u * ch, x);
+          tmem_ld_x32(t_acc + 128u * hh + 32u * pc, x);
           tmem_wait_ld();
-          if (live) {
-            const long long off = m * part.ld_c + static_cast<long long>(tile_n) * kTN + 32 * ch;
-            if (part.c_f32) {
-              float4* dst = reinterpret_cast<float4*>(static_cast<float*>(part.c) + off);
+          uint32_t src;
+          if (part.c_f32) {
+            // 128-byte rows, 128-byte swizzle, two 4 KB blocks
+            const int buf = pc & 1;
+            if (lane == 0) bulk_wait_group_read<1>();  // the store that last used this block has read it
+            __syncwarp();
+            uint4* st = stage + buf * 256;
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                dst[i] = make_float4(__uint_as_float(x[4 * i]), __uint_as_float(x[4 * i + 1]),
-                                     __uint_as_float(x[4 * i + 2]), __uint_as_float(x[4 * i + 3]));
-            } else {
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(part.c) + off);
+            for (int i = 0; i < 8; ++i)
+              st[lane * 8 + (i ^ (lane & 7))] = make_uint4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+            src = stage_addr + buf * 4096;
+          } else {
+            // 64-byte rows, 64-byte swizzle, four 2 KB blocks
+            const int buf = pc & 3;
+            if (lane == 0) bulk_wait_group_read<3>();
+            __syncwarp();
+            uint4* st = stage + buf * 128;
+            const int sw = (lane >> 1) & 3;
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                dst[i] = make_uint4(pack_clamped(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
-                                    pack_clamped(__uint_as_float(x[8 * i + 2]), __uint_as_float(x[8 * i + 3])),
-                                    pack_clamped(__uint_as_float(x[8 * i + 4]), __uint_as_float(x[8 * i + 5])),
-                                    pack_clamped(__uint_as_float(x[8 * i + 6]), __uint_as_float(x[8 * i + 7])));
-            }
+            for (int i = 0; i < 4; ++i)
+              st[lane * 4 + (i ^ sw)] =
+                  make_uint4(pack_clamped(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
+                             pack_clamped(__uint_as_float(x[8 * i + 2]), __uint_as_float(x[8 * i + 3])),
+                             pack_clamped(__uint_as_float(x[8 * i + 4]), __uint_as_float(x[8 * i + 5])),
+                             pack_clamped(__uint_as_float(x[8 * i + 6]), __uint_as_float(x[8 * i + 7])));
+            src = stage_addr + buf * 2048;
+          }
+          fence_proxy_async_smem();  // this thread's writes, for the TMA engine
+          __syncwarp();
+          if (lane == 0 && row0 < a.m) {
+            tma_store_2d(tm_c, src, col_base + 32 * pc, row0);
+            bulk_commit_group();
           }
         }
       } else {
@@ -346,6 +375,8 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(cluster_map(bar(kBarAccEmpty + b), 0));
     }
+    if (lane == 0) bulk_wait_group<0>();  // tile stores still in flight read this CTA's shared memory
+    __syncwarp();
   }
 
   // Neither CTA may leave while the other can still read its shared memory or signal its

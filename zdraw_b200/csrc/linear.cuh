@@ -39,6 +39,10 @@ struct LinearArgs {
 struct LinearMaps {
   CUtensorMap a;
   CUtensorMap w[kMaxLinearParts];  // unused entries repeat w[0]
+  // Plain parts: C as a 2-D map (columns, rows) with a box of 32 columns x 32 rows, 128-byte
+  // swizzle for f32 and 64-byte swizzle for f16, for the epilogue's tile stores. Unused entries
+  // hold any valid map.
+  CUtensorMap c[kMaxLinearParts];
 };
 
 cudaError_t linear_configure();

@@ -132,6 +132,25 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                : "memory");
 }
 
+// Tile store shared -> global through a tensor map (completion tracked by bulk groups of the
+// issuing thread). x is the innermost coordinate: x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src),
+               "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most kPending of this thread's bulk groups have not finished READING shared memory.
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+// Wait until at most kPending of this thread's bulk groups are incomplete (writes performed).
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(kPending) : "memory");
+}
+
 // ---------------------------------------------------------------- CTA pairs (cluster of two)
 // Rank of this CTA in its cluster, cluster-wide barrier, and the shared::cluster address of a
 // shared-memory location in the CTA of a given rank.
