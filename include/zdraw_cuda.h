@@ -309,11 +309,12 @@ ZDRAW_CUDA_API int zdraw_cuda_qkv_projection(void *ctx, void *stream, const void
 /*
  * Wide-head attention: one head, head_dim 512 - the VAE mid-block attention (16384 tokens at
  * 1024 px). Replaces mvattn_owned.run in its product tier (src/metal/mvattn_owned.zig:259-330:
- * half Q, K, V^T; S = Q K^T with f32 output; f32 row softmax with scale 1/sqrt(head_dim) writing
- * half P; O = P V with f32 output), full, non-causal, no mask. q, k, v, o are DEVICE pointers to
- * [tokens][head_dim] f32. tokens and head_dim must be multiples of 256 and tokens <= 32768, else
- * the call is declined. Scratch (half operands, tokens^2 f32 scores, tokens^2 half probabilities:
- * 1.6 GB at 16384 tokens) is grow-only context memory.
+ * half Q, K, V^T; S = Q K^T with f32 accumulation; f32 row softmax with scale 1/sqrt(head_dim)
+ * giving half P; O = P V with f32 output), full, non-causal, no mask. q, k, v, o are DEVICE
+ * pointers to [tokens][head_dim] f32. tokens and head_dim must be multiples of 256 and
+ * tokens <= 32768, else the call is declined. Scratch (half operands, tokens^2 half exp(scores),
+ * row statistics: 0.6 GB at 16384 tokens) is grow-only context memory; the f32 scores are never
+ * stored.
  */
 ZDRAW_CUDA_API int zdraw_cuda_wide_attention(void *ctx, void *stream, const float *q, const float *k, const float *v,
                                              float *o, size_t tokens, size_t head_dim);

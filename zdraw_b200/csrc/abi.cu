@@ -54,7 +54,7 @@ struct Ctx {
   // Grow-only scratch (device memory).
   Buf q16, k16, v16, tile_list;
   Buf st_q, st_k, st_v, st_o, st_w, st_cos, st_sin, st_mask;  // staging for the host-buffer path
-  Buf wa_q16, wa_k16, wa_vt16, wa_s, wa_p;                     // wide-head attention: half operands, scores, probabilities
+  Buf wa_q16, wa_k16, wa_vt16, wa_aux, wa_p;  // wide-head attention: half operands, row statistics, exp(scores)
   char err[256] = {0};
 };
 
@@ -385,7 +385,7 @@ int zdraw_cuda_attn_destroy(void* ctx) {
   cudaDeviceSynchronize();
   Buf* bufs[] = {&c->q16, &c->k16, &c->v16, &c->tile_list, &c->st_q, &c->st_k, &c->st_v,
                  &c->st_o, &c->st_w, &c->st_cos, &c->st_sin, &c->st_mask,
-                 &c->wa_q16, &c->wa_k16, &c->wa_vt16, &c->wa_s, &c->wa_p};
+                 &c->wa_q16, &c->wa_k16, &c->wa_vt16, &c->wa_aux, &c->wa_p};
   for (Buf* b : bufs)
     if (b->p) cudaFree(b->p);
   if (c->d_status) cudaFree(c->d_status);
@@ -629,8 +629,12 @@ namespace {
 struct PartSpec {
   const void* w;
   void* c;
-  uint32_t epilogue;  // 0 plain, 1 qk
+  uint32_t epilogue;  // zdraw::kEpilogue*: 0 plain, 1 qk; 2 row max and 3 exp are internal (wide attention)
   const float *w_txt, *w_img;
+  const float* row_scale = nullptr;  // plain: optional factor per row
+  unsigned int* row_key = nullptr;   // row max / exp: ordered keys of the row maxima
+  float* row_sum = nullptr;          // exp: partial row sums
+  float exp_scale = 0.0f;
 };
 
 // Shared body of zdraw_cuda_linear and zdraw_cuda_qkv_projection: validates, builds the tensor
@@ -643,7 +647,7 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
   if (!a || !aligned16(a)) return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned matrix");
   bool any_qk = false;
   for (int i = 0; i < n_parts; ++i) {
-    if (parts[i].epilogue > 1) return fail(cx, ZDRAW_CUDA_E_ARG, "bad epilogue");
+    if (parts[i].epilogue > 3) return fail(cx, ZDRAW_CUDA_E_ARG, "bad epilogue");
     if (!parts[i].w || !parts[i].c || !aligned16(parts[i].w) || !aligned16(parts[i].c))
       return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned matrix");
     any_qk = any_qk || parts[i].epilogue == 1;
@@ -690,6 +694,10 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
     } else {
       lp.c_f32 = p->c_dtype == ZDRAW_DTYPE_F32;
       lp.ld_c = ld_c;
+      lp.row_scale = parts[i].row_scale;
+      lp.row_key = parts[i].row_key;
+      lp.row_sum = parts[i].row_sum;
+      lp.exp_scale = parts[i].exp_scale;
     }
   }
   ZD_CUDA(cx, cudaSetDevice(cx->device));
@@ -712,7 +720,7 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
   // Plain parts: C for the epilogue's tile stores (32 columns x 32 rows, swizzle of the row size).
   for (int i = 0; i < zdraw::kMaxLinearParts; ++i) {
     maps.c[i] = maps.a;  // any valid map where none is used
-    if (i >= n_parts || parts[i].epilogue != 0) continue;
+    if (i >= n_parts || (parts[i].epilogue != 0 && parts[i].epilogue != 3)) continue;
     const bool f32 = p->c_dtype == ZDRAW_DTYPE_F32;
     const cuuint64_t dims[2] = {p->n, p->m};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_c) * (f32 ? 4u : 2u)};
@@ -737,6 +745,7 @@ int zdraw_cuda_linear(void* ctx, void* stream, const void* a, const void* w, voi
   Ctx* cx = as_ctx(ctx);
   if (!cx) return ZDRAW_CUDA_E_ARG;
   if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
+  if (p->epilogue > 1) return fail(cx, ZDRAW_CUDA_E_ARG, "bad epilogue");
   if (p->epilogue == 1 && p->c_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_E_ARG, "the qk epilogue writes f16");
   const PartSpec part = {w, c, p->epilogue, norm_w_txt, norm_w_img};
   return run_linear(cx, stream, a, 1, &part, rope_cos, rope_sin, p);
@@ -756,10 +765,15 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
     return fail(cx, ZDRAW_CUDA_DECLINED, "tokens and head_dim must be multiples of 256, tokens <= 32768");
   ZD_CUDA(cx, cudaSetDevice(cx->device));
   const size_t n = tokens * head_dim;
+  const size_t n_partial = 2 * (tokens / 256);  // partial row sums: one per 128-column half tile
+  const size_t aux_bytes = tokens * 4 * (2 + n_partial);  // row keys, 1/row sum, partial sums
   int rc;
   if ((rc = ensure(cx, cx->wa_q16, n * 2)) || (rc = ensure(cx, cx->wa_k16, n * 2)) || (rc = ensure(cx, cx->wa_vt16, n * 2)) ||
-      (rc = ensure(cx, cx->wa_s, tokens * tokens * 4)) || (rc = ensure(cx, cx->wa_p, tokens * tokens * 2)))
+      (rc = ensure(cx, cx->wa_aux, aux_bytes)) || (rc = ensure(cx, cx->wa_p, tokens * tokens * 2)))
     return rc;
+  unsigned int* row_key = static_cast<unsigned int*>(cx->wa_aux.p);
+  float* row_inv = reinterpret_cast<float*>(row_key + tokens);
+  float* row_sum = row_inv + tokens;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // kf32_to_h x2, kvt_transpose_h (mvattn_owned.zig:322-330)
   ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16(st, q, cx->wa_q16.p, static_cast<long long>(tokens), static_cast<int>(head_dim),
@@ -767,26 +781,33 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16(st, k, cx->wa_k16.p, static_cast<long long>(tokens), static_cast<int>(head_dim),
                                             static_cast<long long>(head_dim)));
   ZD_CUDA(cx, zdraw::launch_transpose_cast(st, v, cx->wa_vt16.p, static_cast<int>(tokens), static_cast<int>(head_dim)));
-  // S[tokens, tokens] = Q K^T (K is already [n][k]), f32 out
+  ZD_CUDA(cx, cudaMemsetAsync(row_key, 0, tokens * 4, st));  // key 0 lies below every float
+  // The scores S = Q K^T (K is already [n][k]) are never stored. A first product keeps only each
+  // row's maximum; a second one turns its accumulator into exp(scale (S - max)) in half and keeps
+  // partial row sums of what it stored: recomputing S (k = head_dim is short) costs less than
+  // writing and re-reading tokens^2 f32 scores.
   zdraw_cuda_linear_params ps = {};
   ps.m = static_cast<uint32_t>(tokens);
   ps.n = static_cast<uint32_t>(tokens);
   ps.k = static_cast<uint32_t>(head_dim);
-  ps.a_dtype = ps.w_dtype = ZDRAW_DTYPE_F16;
-  ps.c_dtype = ZDRAW_DTYPE_F32;
-  const PartSpec part_s = {cx->wa_k16.p, cx->wa_s.p, 0, nullptr, nullptr};
+  ps.a_dtype = ps.w_dtype = ps.c_dtype = ZDRAW_DTYPE_F16;
+  PartSpec part_s = {cx->wa_k16.p, cx->wa_p.p, static_cast<uint32_t>(zdraw::kEpilogueRowMax), nullptr, nullptr};
+  part_s.row_key = row_key;
   if ((rc = run_linear(cx, stream, cx->wa_q16.p, 1, &part_s, nullptr, nullptr, &ps)) != 0) return rc;
-  // P = softmax(S / sqrt(head_dim)) in half
-  ZD_CUDA(cx, zdraw::launch_row_softmax(st, static_cast<const float*>(cx->wa_s.p), cx->wa_p.p, static_cast<long long>(tokens),
-                                        static_cast<int>(tokens), 1.0f / std::sqrt(static_cast<float>(head_dim))));
-  // O[tokens, head_dim] = P (V^T)^T, f32 out
+  part_s.epilogue = static_cast<uint32_t>(zdraw::kEpilogueExp);
+  part_s.row_sum = row_sum;
+  part_s.exp_scale = 1.4426950408889634f / std::sqrt(static_cast<float>(head_dim));
+  if ((rc = run_linear(cx, stream, cx->wa_q16.p, 1, &part_s, nullptr, nullptr, &ps)) != 0) return rc;
+  ZD_CUDA(cx, zdraw::launch_row_sum_inverse(st, row_sum, static_cast<int>(n_partial), static_cast<long long>(tokens), row_inv));
+  // O[tokens, head_dim] = (P (V^T)^T) / row sum, f32 out
   zdraw_cuda_linear_params po = {};
   po.m = static_cast<uint32_t>(tokens);
   po.n = static_cast<uint32_t>(head_dim);
   po.k = static_cast<uint32_t>(tokens);
   po.a_dtype = po.w_dtype = ZDRAW_DTYPE_F16;
   po.c_dtype = ZDRAW_DTYPE_F32;
-  const PartSpec part_o = {cx->wa_vt16.p, o, 0, nullptr, nullptr};
+  PartSpec part_o = {cx->wa_vt16.p, o, 0, nullptr, nullptr};
+  part_o.row_scale = row_inv;
   return run_linear(cx, stream, cx->wa_p.p, 1, &part_o, nullptr, nullptr, &po);
 }
 

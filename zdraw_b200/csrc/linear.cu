@@ -81,6 +81,16 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
   }
 }
 
+// Order-preserving map float -> unsigned (0 lies below every float), so that a row maximum can be
+// taken with atomicMax, which does not depend on the order of the updates.
+__device__ __forceinline__ uint32_t float_key(float x) {
+  const uint32_t b = __float_as_uint(x);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
 __device__ __forceinline__ uint32_t pack_clamped(float lo, float hi) {
   const __half2 lim = __float2half2_rn(kHalfMax);
   __half2 h = __floats2half2_rn(lo, hi);
@@ -231,7 +241,19 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
       const long long m = static_cast<long long>(tile_m) * kTM + row;
       const bool live = m < a.m;
 
-      if (part.epilogue == kEpiloguePlain) {
+      if (part.epilogue == kEpilogueRowMax) {
+        // Row maximum of the tile's columns, nothing stored: each thread reduces its 128 columns.
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int pc = 0; pc < 4; ++pc) {
+          uint32_t x[32];
+          tmem_ld_x32(t_acc + 128u * hh + 32u * pc, x);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+        }
+        if (live) atomicMax(part.row_key + m, float_key(mx));
+      } else if (part.epilogue == kEpiloguePlain || part.epilogue == kEpilogueExp) {
         // A thread holds consecutive columns of ITS row, and rows lie ld_c apart, so storing from
         // registers would touch 32 different lines per instruction. Instead the warp parks its
         // 32 rows x 32 columns in shared memory in the tensor map's swizzle (128-byte rows of f32,
@@ -243,6 +265,15 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
         const uint32_t stage_addr = base + kOffTab + (warp - 4) * kTabBytesPerWarp;
         const int row0 = tile_m * kTM + quarter * 32;  // first row of this warp
         const int col_base = tile_n * kTN + 128 * hh;
+        const bool exp_mode = part.epilogue == kEpilogueExp;
+        // plain: optional factor of this row; exp: x -> exp2(x * c + bias), bias = -max * c
+        float mul = 1.0f, bias = 0.0f, psum = 0.0f;
+        if (exp_mode) {
+          mul = part.exp_scale;
+          bias = live ? -key_float(part.row_key[m]) * part.exp_scale : 0.0f;
+        } else if (part.row_scale != nullptr && live) {
+          mul = part.row_scale[m];
+        }
 #pragma unroll 1
         for (int pc = 0; pc < 4; ++pc) {  // 32 columns of this warp's 128 at a time
           uint32_t x[32];
@@ -257,7 +288,9 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
             uint4* st = stage + buf * 256;
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              st[lane * 8 + (i ^ (lane & 7))] = make_uint4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+              st[lane * 8 + (i ^ (lane & 7))] =
+                  make_uint4(__float_as_uint(__uint_as_float(x[4 * i]) * mul), __float_as_uint(__uint_as_float(x[4 * i + 1]) * mul),
+                             __float_as_uint(__uint_as_float(x[4 * i + 2]) * mul), __float_as_uint(__uint_as_float(x[4 * i + 3]) * mul));
             src = stage_addr + buf * 4096;
           } else {
             // 64-byte rows, 64-byte swizzle, four 2 KB blocks
@@ -266,13 +299,23 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
             __syncwarp();
             uint4* st = stage + buf * 128;
             const int sw = (lane >> 1) & 3;
+            uint32_t h[16];
+            if (exp_mode) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              st[lane * 4 + (i ^ sw)] =
-                  make_uint4(pack_clamped(__uint_as_float(x[8 * i]), __uint_as_float(x[8 * i + 1])),
-                             pack_clamped(__uint_as_float(x[8 * i + 2]), __uint_as_float(x[8 * i + 3])),
-                             pack_clamped(__uint_as_float(x[8 * i + 4]), __uint_as_float(x[8 * i + 5])),
-                             pack_clamped(__uint_as_float(x[8 * i + 6]), __uint_as_float(x[8 * i + 7])));
+              for (int i = 0; i < 16; ++i) {
+                const float e0 = ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias));
+                const float e1 = ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias));
+                psum += e0 + e1;  // f32 sum of the unrounded values, as the reference's softmax takes it
+                const __half2 v = __floats2half2_rn(e0, e1);
+                h[i] = *reinterpret_cast<const uint32_t*>(&v);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                h[i] = pack_clamped(__uint_as_float(x[2 * i]) * mul, __uint_as_float(x[2 * i + 1]) * mul);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) st[lane * 4 + (i ^ sw)] = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
             src = stage_addr + buf * 2048;
           }
           fence_proxy_async_smem();  // this thread's writes, for the TMA engine
@@ -282,6 +325,7 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
             bulk_commit_group();
           }
         }
+        if (exp_mode && live) part.row_sum[m * (2 * tiles_n) + 2 * tile_n + hh] = psum;
       } else {
         // qk epilogue: the tile's 256 columns are two heads of this token's projection.
         const long long mm = live ? m : 0;

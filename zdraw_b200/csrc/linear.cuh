@@ -7,8 +7,10 @@
 
 namespace zdraw {
 
-constexpr int kEpiloguePlain = 0;
-constexpr int kEpilogueQk = 1;
+constexpr int kEpiloguePlain = 0;   // C = A W^T (times row_scale[row] when given)
+constexpr int kEpilogueQk = 1;      // q/k prologue applied to the accumulator
+constexpr int kEpilogueRowMax = 2;  // no C: row_key[row] = max over the row, as an ordered key
+constexpr int kEpilogueExp = 3;     // C = half(exp2((A W^T - max[row]) * exp_scale)), partial row sums
 
 constexpr int kMaxLinearParts = 3;
 
@@ -19,6 +21,13 @@ struct LinearPart {
   void* c;       // plain: [m][ld_c]; qk: f16 head-major [image][head][token][128]
   long long ld_c;
   const float *w_txt, *w_img;  // qk: norm weights [128]
+  // plain: optional per-row factor [m]. row max: out, one ordered key per row (see float_key), zeroed
+  // by the caller. exp: in, the same keys; row_sum receives [m][2 * n / 256] partial sums of the
+  // exponentials (f32, before rounding to half), one per 128-column half tile.
+  const float* row_scale;
+  unsigned int* row_key;
+  float* row_sum;
+  float exp_scale;
 };
 
 // Up to three products that share A (the Q, K and V projections of one activation) run as one

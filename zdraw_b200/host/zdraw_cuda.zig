@@ -138,6 +138,16 @@ pub extern fn zdraw_cuda_qkv_projection(
     rope_sin: [*]const f32,
     params: *const LinearParams,
 ) c_int;
+pub extern fn zdraw_cuda_wide_attention(
+    ctx: *anyopaque,
+    stream: ?*anyopaque,
+    q: [*]const f32,
+    k: [*]const f32,
+    v: [*]const f32,
+    o: [*]f32,
+    tokens: usize,
+    head_dim: usize,
+) c_int;
 pub extern fn zdraw_cuda_attention_host(
     ctx: *anyopaque,
     q: *const anyopaque,
