@@ -387,8 +387,8 @@ def main():
         ms_w = timed(wide_step)
         wide = {"api": "zdraw_cuda_wide_attention", "tokens": wt, "head_dim": wd, "ms_per_call": ms_w,
                 "achieved": 4.0 * wt * wt * wd / ms_w / 1e9, "unit": "TFLOP/s",
-                "kernels": "2 casts, transpose, linear_kernel x3 (row max of S; exp(S - max) in half + row sums; "
-                           "P V / row sum), row_sum_inverse_kernel",
+                "kernels": "2 casts (half + e4m3), transpose, linear_kernel x3 (row max of S on e4m3 operands; "
+                           "exp(S - max) in half + row sums; P V / row sum), row_sum_inverse_kernel",
                 "l2": "exp(scores) in half (0.5 GB) streams through HBM once each way"}
         del wq, wk, wv, wo
         if ctx.last_status() != 0:

@@ -313,8 +313,8 @@ ZDRAW_CUDA_API int zdraw_cuda_qkv_projection(void *ctx, void *stream, const void
  * giving half P; O = P V with f32 output), full, non-causal, no mask. q, k, v, o are DEVICE
  * pointers to [tokens][head_dim] f32. tokens and head_dim must be multiples of 256 and
  * tokens <= 32768, else the call is declined. Scratch (half operands, tokens^2 half exp(scores),
- * row statistics: 0.6 GB at 16384 tokens) is grow-only context memory; the f32 scores are never
- * stored.
+ * e4m3 copies of Q and K for a first estimate of the row maxima, row statistics: 0.6 GB at 16384
+ * tokens) is grow-only context memory; the f32 scores are never stored.
  */
 ZDRAW_CUDA_API int zdraw_cuda_wide_attention(void *ctx, void *stream, const float *q, const float *k, const float *v,
                                              float *o, size_t tokens, size_t head_dim);

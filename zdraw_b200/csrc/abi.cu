@@ -55,6 +55,7 @@ struct Ctx {
   Buf q16, k16, v16, tile_list;
   Buf st_q, st_k, st_v, st_o, st_w, st_cos, st_sin, st_mask;  // staging for the host-buffer path
   Buf wa_q16, wa_k16, wa_vt16, wa_aux, wa_p;  // wide-head attention: half operands, row statistics, exp(scores)
+  Buf wa_q8, wa_k8;                            // e4m3 copies of Q and K for the row-max pass
   char err[256] = {0};
 };
 
@@ -385,7 +386,7 @@ int zdraw_cuda_attn_destroy(void* ctx) {
   cudaDeviceSynchronize();
   Buf* bufs[] = {&c->q16, &c->k16, &c->v16, &c->tile_list, &c->st_q, &c->st_k, &c->st_v,
                  &c->st_o, &c->st_w, &c->st_cos, &c->st_sin, &c->st_mask,
-                 &c->wa_q16, &c->wa_k16, &c->wa_vt16, &c->wa_aux, &c->wa_p};
+                 &c->wa_q16, &c->wa_k16, &c->wa_vt16, &c->wa_aux, &c->wa_p, &c->wa_q8, &c->wa_k8};
   for (Buf* b : bufs)
     if (b->p) cudaFree(b->p);
   if (c->d_status) cudaFree(c->d_status);
@@ -639,8 +640,10 @@ struct PartSpec {
 
 // Shared body of zdraw_cuda_linear and zdraw_cuda_qkv_projection: validates, builds the tensor
 // maps and launches one kernel that computes every part from the same A.
+// operands_e4m3 (internal, the row-max pass of the wide attention): A and W hold e4m3 bytes instead
+// of halves; p->a_dtype / w_dtype still say f16 and strides count elements.
 int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec* parts, const float* rope_cos,
-               const float* rope_sin, const zdraw_cuda_linear_params* p) {
+               const float* rope_sin, const zdraw_cuda_linear_params* p, bool operands_e4m3 = false) {
   if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
   if (p->reserved != 0 || p->m == 0 || p->n == 0 || p->k == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero size or reserved != 0");
   if (p->c_dtype != ZDRAW_DTYPE_F16 && p->c_dtype != ZDRAW_DTYPE_F32) return fail(cx, ZDRAW_CUDA_E_ARG, "bad c_dtype");
@@ -656,16 +659,20 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
   // admit 32-aligned dims only, src/metal/mres_util.zig:30-38).
   if (p->a_dtype != ZDRAW_DTYPE_F16 || p->w_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_DECLINED, "A and W must be f16");
   if (p->n % 256 != 0 || p->k % 64 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "n must be a multiple of 256 and k of 64");
+  if (operands_e4m3 && p->k % 128 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "k must be a multiple of 128 for 8-bit operands");
   if (p->m > (1u << 30) || p->n > (1u << 30) || p->k > (1u << 30)) return fail(cx, ZDRAW_CUDA_DECLINED, "shape too large");
   const long long ld_a = p->ld_a ? static_cast<long long>(p->ld_a) : p->k;
   const long long ld_w = p->ld_w ? static_cast<long long>(p->ld_w) : p->k;
   const long long ld_c = p->ld_c ? static_cast<long long>(p->ld_c) : p->n;
   if (ld_a < p->k || ld_w < p->k || ld_c < p->n) return fail(cx, ZDRAW_CUDA_E_ARG, "row stride smaller than the row");
-  if (ld_a % 8 != 0 || ld_w % 8 != 0 || ld_c % 8 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "row strides must be multiples of 8");
+  const long long ld_align = operands_e4m3 ? 16 : 8;  // TMA strides are multiples of 16 bytes
+  if (ld_a % ld_align != 0 || ld_w % ld_align != 0 || ld_c % 8 != 0)
+    return fail(cx, ZDRAW_CUDA_DECLINED, "row strides must be multiples of 8 elements (16 for 8-bit operands)");
   zdraw::LinearArgs la = {};
   la.m = static_cast<int>(p->m);
   la.n = static_cast<int>(p->n);
   la.k = static_cast<int>(p->k);
+  la.fp8 = operands_e4m3 ? 1 : 0;
   la.n_parts = n_parts;
   la.status = cx->d_status;
   if (any_qk) {
@@ -701,15 +708,17 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
     }
   }
   ZD_CUDA(cx, cudaSetDevice(cx->device));
-  // Row-major f16 matrices [rows][ld] as tiled tensor maps: boxes of 64 columns x 128 rows.
+  // Row-major matrices [rows][ld] as tiled tensor maps: boxes of 128 bytes (64 halves) x 128 rows.
   zdraw::LinearMaps maps;
   const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const cuuint64_t esz = operands_e4m3 ? 1u : 2u;
   auto encode = [&](CUtensorMap* tm, const void* base_ptr, uint64_t rows, long long ld) {
     const cuuint64_t dims[4] = {p->k, rows, 1, 1};
-    const cuuint64_t strides[3] = {2ull * static_cast<cuuint64_t>(ld), 2ull * static_cast<cuuint64_t>(ld) * rows,
-                                   2ull * static_cast<cuuint64_t>(ld) * rows};
-    const cuuint32_t box[4] = {64, 128, 1, 1};
-    return cx->encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base_ptr), dims, strides, box, estr,
+    const cuuint64_t strides[3] = {esz * static_cast<cuuint64_t>(ld), esz * static_cast<cuuint64_t>(ld) * rows,
+                                   esz * static_cast<cuuint64_t>(ld) * rows};
+    const cuuint32_t box[4] = {operands_e4m3 ? 128u : 64u, 128, 1, 1};  // 128-byte rows either way
+    return cx->encode(tm, operands_e4m3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                      const_cast<void*>(base_ptr), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
@@ -769,23 +778,25 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   const size_t aux_bytes = tokens * 4 * (2 + n_partial);  // row keys, 1/row sum, partial sums
   int rc;
   if ((rc = ensure(cx, cx->wa_q16, n * 2)) || (rc = ensure(cx, cx->wa_k16, n * 2)) || (rc = ensure(cx, cx->wa_vt16, n * 2)) ||
-      (rc = ensure(cx, cx->wa_aux, aux_bytes)) || (rc = ensure(cx, cx->wa_p, tokens * tokens * 2)))
+      (rc = ensure(cx, cx->wa_aux, aux_bytes)) || (rc = ensure(cx, cx->wa_p, tokens * tokens * 2)) ||
+      (rc = ensure(cx, cx->wa_q8, n)) || (rc = ensure(cx, cx->wa_k8, n)))
     return rc;
   unsigned int* row_key = static_cast<unsigned int*>(cx->wa_aux.p);
   float* row_inv = reinterpret_cast<float*>(row_key + tokens);
   float* row_sum = row_inv + tokens;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // kf32_to_h x2, kvt_transpose_h (mvattn_owned.zig:322-330)
-  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16(st, q, cx->wa_q16.p, static_cast<long long>(tokens), static_cast<int>(head_dim),
-                                            static_cast<long long>(head_dim)));
-  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16(st, k, cx->wa_k16.p, static_cast<long long>(tokens), static_cast<int>(head_dim),
-                                            static_cast<long long>(head_dim)));
+  // kf32_to_h x2, kvt_transpose_h (mvattn_owned.zig:322-330); Q and K also as e4m3 (see below)
+  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16_e4m3(st, q, cx->wa_q16.p, cx->wa_q8.p, static_cast<long long>(n)));
+  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16_e4m3(st, k, cx->wa_k16.p, cx->wa_k8.p, static_cast<long long>(n)));
   ZD_CUDA(cx, zdraw::launch_transpose_cast(st, v, cx->wa_vt16.p, static_cast<int>(tokens), static_cast<int>(head_dim)));
   ZD_CUDA(cx, cudaMemsetAsync(row_key, 0, tokens * 4, st));  // key 0 lies below every float
   // The scores S = Q K^T (K is already [n][k]) are never stored. A first product keeps only each
   // row's maximum; a second one turns its accumulator into exp(scale (S - max)) in half and keeps
-  // partial row sums of what it stored: recomputing S (k = head_dim is short) costs less than
-  // writing and re-reading tokens^2 f32 scores.
+  // partial row sums: recomputing S (k = head_dim is short) costs less than writing and re-reading
+  // tokens^2 f32 scores. Softmax does not change when another number than the exact maximum is
+  // subtracted, as long as nothing overflows, so the first product runs on e4m3 copies of Q and K
+  // at twice the rate: its maxima are a few percent of |S| off, and the exponentials are clamped
+  // to the half range.
   zdraw_cuda_linear_params ps = {};
   ps.m = static_cast<uint32_t>(tokens);
   ps.n = static_cast<uint32_t>(tokens);
@@ -793,7 +804,9 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   ps.a_dtype = ps.w_dtype = ps.c_dtype = ZDRAW_DTYPE_F16;
   PartSpec part_s = {cx->wa_k16.p, cx->wa_p.p, static_cast<uint32_t>(zdraw::kEpilogueRowMax), nullptr, nullptr};
   part_s.row_key = row_key;
-  if ((rc = run_linear(cx, stream, cx->wa_q16.p, 1, &part_s, nullptr, nullptr, &ps)) != 0) return rc;
+  part_s.w = cx->wa_k8.p;
+  if ((rc = run_linear(cx, stream, cx->wa_q8.p, 1, &part_s, nullptr, nullptr, &ps, true)) != 0) return rc;
+  part_s.w = cx->wa_k16.p;
   part_s.epilogue = static_cast<uint32_t>(zdraw::kEpilogueExp);
   part_s.row_sum = row_sum;
   part_s.exp_scale = 1.4426950408889634f / std::sqrt(static_cast<float>(head_dim));

@@ -27,6 +27,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <type_traits>
+
 #include "ptx.cuh"
 
 namespace zdraw {
@@ -113,7 +115,8 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
   const int tiles_n = a.n / kTN;                        // column blocks of one part
   const int tiles_m = (a.m + 2 * kTM - 1) / (2 * kTM);  // pair tiles: 256 rows
   const int n_tiles = tiles_m * tiles_n * a.n_parts;
-  const int k_steps = a.k / kTK;
+  const int k_steps = a.fp8 ? a.k / (2 * kTK) : a.k / kTK;  // a stage is a 128-byte slice of K per row
+  const int k_per_stage = a.fp8 ? 2 * kTK : kTK;
 
   if (threadIdx.x == 0) {
     // Both CTAs of a pair take every collective step below whatever happens, so a failed wait
@@ -172,8 +175,8 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
           // Both CTAs' bytes are counted on the even CTA's barrier, which expects all of them.
           const uint32_t full = cluster_map(bar(kBarFull + stage), 0);
           if (rank == 0) mbar_arrive_expect_tx(bar(kBarFull + stage), 2 * kStageBytes);
-          tma_load_4d_pair(dst, &maps.a, full, ks * kTK, row_a, 0, 0);
-          tma_load_4d_pair(dst + kABytes, tm_w, full, ks * kTK, row_w, 0, 0);
+          tma_load_4d_pair(dst, &maps.a, full, ks * k_per_stage, row_a, 0, 0);
+          tma_load_4d_pair(dst + kABytes, tm_w, full, ks * k_per_stage, row_w, 0, 0);
         }
       }
       if (!ok) {
@@ -196,18 +199,32 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + 256u * b;
-        for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const uint32_t stage = it % kStages;
-          const uint32_t phase = (it / kStages) & 1u;
-          ok = wait_bar(bar(kBarFull + stage), phase, abort_flag, a.status);
-          if (!ok) break;
-          const uint32_t a_addr = base + stage * kStageBytes;
-          const uint64_t desc_a = smem_desc_sw128(a_addr, 16, 1024);
-          const uint64_t desc_b = smem_desc_sw128(a_addr + kABytes, 16, 1024);
+        // One K walk per operand type, so that the issuing thread's loop holds no type test.
+        auto walk_k = [&](auto is_fp8) {
+          for (int ks = 0; ks < k_steps; ++ks, ++it) {
+            const uint32_t stage = it % kStages;
+            const uint32_t phase = (it / kStages) & 1u;
+            ok = wait_bar(bar(kBarFull + stage), phase, abort_flag, a.status);
+            if (!ok) break;
+            const uint32_t a_addr = base + stage * kStageBytes;
+            const uint64_t desc_a = smem_desc_sw128(a_addr, 16, 1024);
+            const uint64_t desc_b = smem_desc_sw128(a_addr + kABytes, 16, 1024);
+            // Four MMAs per stage, each 32 bytes further along the swizzled rows: K = 16 halves
+            // or 32 e4m3 bytes.
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            umma_ss_pair(d_tmem, desc_a + 2u * kk, desc_b + 2u * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
-          umma_commit_pair(bar(kBarEmpty + stage), 3);  // both CTAs' producers may refill the stage
+            for (int kk = 0; kk < 4; ++kk) {
+              if constexpr (decltype(is_fp8)::value)
+                umma_ss_pair_f8(d_tmem, desc_a + 2u * kk, desc_b + 2u * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+              else
+                umma_ss_pair(d_tmem, desc_a + 2u * kk, desc_b + 2u * kk, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            }
+            umma_commit_pair(bar(kBarEmpty + stage), 3);  // both CTAs' producers may refill the stage
+          }
+        };
+        if (a.fp8) {
+          walk_k(std::true_type{});
+        } else {
+          walk_k(std::false_type{});
         }
         if (!ok) break;
         umma_commit_pair(bar(kBarAccFull + b), 3);  // both CTAs' epilogues may read their rows
@@ -303,8 +320,9 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
             if (exp_mode) {
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                const float e0 = ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias));
-                const float e1 = ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias));
+                // (the subtracted maximum may be an estimate: keep the result in the half range)
+                const float e0 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias)), kHalfMax);
+                const float e1 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias)), kHalfMax);
                 psum += e0 + e1;  // f32 sum of the unrounded values, as the reference's softmax takes it
                 const __half2 v = __floats2half2_rn(e0, e1);
                 h[i] = *reinterpret_cast<const uint32_t*>(&v);

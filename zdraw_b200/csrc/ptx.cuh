@@ -209,6 +209,19 @@ __device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t a_desc, u
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with 8-bit floating-point operands (e4m3 when the descriptor's format fields are 0):
+// K = 32 elements per instruction, f32 accumulation.
+__device__ __forceinline__ void umma_ss_pair_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // When every MMA issued so far has finished, arrive once on the mbarrier at this shared-memory
 // offset in each CTA named by cta_mask.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {

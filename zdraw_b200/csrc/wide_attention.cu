@@ -7,6 +7,7 @@
 #include "wide_attention.cuh"
 
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 namespace zdraw {
 
@@ -37,6 +38,27 @@ __global__ void __launch_bounds__(256) transpose_cast_kernel(const float* __rest
   }
 }
 
+// Four floats per thread -> four halves (clamped) and four e4m3 bytes (saturating): the operand
+// is read once for both copies.
+__global__ void __launch_bounds__(256) cast_f32_to_f16_e4m3_kernel(const float4* __restrict__ in, uint2* __restrict__ out16,
+                                                                   uint32_t* __restrict__ out8, long long n4) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 v = in[i];
+  v.x = fminf(fmaxf(v.x, -kHalfMax), kHalfMax);
+  v.y = fminf(fmaxf(v.y, -kHalfMax), kHalfMax);
+  v.z = fminf(fmaxf(v.z, -kHalfMax), kHalfMax);
+  v.w = fminf(fmaxf(v.w, -kHalfMax), kHalfMax);
+  const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+  uint2 o;
+  o.x = *reinterpret_cast<const uint32_t*>(&h0);
+  o.y = *reinterpret_cast<const uint32_t*>(&h1);
+  out16[i] = o;
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x, v.y), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z, v.w), __NV_SATFINITE, __NV_E4M3);
+  out8[i] = lo | (hi << 16);
+}
+
 // One warp per row: lane l adds partial[l], partial[l + 32], ... in order, then the lanes are
 // folded by xor shuffles: the same order on every run.
 __global__ void __launch_bounds__(256) row_sum_inverse_kernel(const float* __restrict__ partial, int n_partial,
@@ -56,6 +78,15 @@ __global__ void __launch_bounds__(256) row_sum_inverse_kernel(const float* __res
 cudaError_t launch_transpose_cast(cudaStream_t stream, const float* in, void* out_f16, int tokens, int ch) {
   const dim3 grid((tokens + 31) / 32, (ch + 31) / 32);
   transpose_cast_kernel<<<grid, 256, 0, stream>>>(in, static_cast<__half*>(out_f16), tokens, ch);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cast_f32_to_f16_e4m3(cudaStream_t stream, const float* in, void* out_f16, void* out_e4m3, long long n) {
+  if (n <= 0) return cudaSuccess;
+  if (n % 4 != 0) return cudaErrorInvalidValue;
+  const long long n4 = n / 4;
+  cast_f32_to_f16_e4m3_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const float4*>(in), static_cast<uint2*>(out_f16), static_cast<uint32_t*>(out_e4m3), n4);
   return cudaGetLastError();
 }
 
