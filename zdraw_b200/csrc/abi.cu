@@ -769,9 +769,9 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   if (tokens == 0 || head_dim == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero tokens or head_dim");
   // Shapes outside the kernels are declined (the reference's own admission is tokens % 32 and
   // head_dim % 32, src/metal/mvattn_owned.zig:271-272): both products run on the 256-column tiles
-  // of the projection kernel and a score row must fit one softmax block.
-  if (tokens % 256 != 0 || head_dim % 256 != 0 || tokens > 32768 || head_dim > 4096)
-    return fail(cx, ZDRAW_CUDA_DECLINED, "tokens and head_dim must be multiples of 256, tokens <= 32768");
+  // of the projection kernel; the token bound keeps the tokens^2 half scratch below 9 GB.
+  if (tokens % 256 != 0 || head_dim % 256 != 0 || tokens > 65536 || head_dim > 4096)
+    return fail(cx, ZDRAW_CUDA_DECLINED, "tokens and head_dim must be multiples of 256, tokens <= 65536");
   ZD_CUDA(cx, cudaSetDevice(cx->device));
   const size_t n = tokens * head_dim;
   const size_t n_partial = 2 * (tokens / 256);  // partial row sums: one per 128-column half tile
