@@ -456,7 +456,11 @@ def main():
                 "peak_source": peaks["source"] + " dense bf16 matmul, burst",
                 "frac_of_sustained": attn_tflops / peaks["bf16_tflops_sustained"],
                 "frac_of_nominal_fp16": attn_tflops / NOMINAL_FP16_TFLOPS,
-                "ms_per_launch": ms_attention, "traffic": None,
+                "ms_per_launch": ms_attention,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch (one ncu capture of this
+                # workload, profiles/attn_fwd_kernel_klein_1024.md); other workloads were not captured.
+                "traffic": 90.5e6 if (w.name == "klein_1024" and not by_heads) else None, "traffic_unit": "B per launch",
+                "algorithmic_bytes": 4 * w.batch * w.tokens * hs.count * 128 * 2,
             },
             "prologue": {"kernel": "qk_norm_rope_kernel", "bound": "hbm", "achieved": prologue_gbs,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": prologue_gbs / peaks["hbm_gbs"],
