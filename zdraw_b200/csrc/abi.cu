@@ -320,9 +320,15 @@ int run_attention(Ctx* c, cudaStream_t stream, const void* q16, const void* k16,
   a.o_tok_stride = o_tok;
   a.o_head_stride = o_head;
   a.o_batch_stride = o_batch;
+  // f16 output leaves through tile stores: o as a tensor map with q's shape rules (token stride
+  // ld_o, or dense head-major).
+  CUtensorMap tm_o = tm_q;
+  a.o_head_major = o_hm ? 1 : 0;
+  a.o_tma = p->out_dtype == ZDRAW_DTYPE_F16 ? 1 : 0;
+  if (a.o_tma && (rc = make_tmap(c, &tm_o, o, o_hm, s, s.ld_o)) != 0) return rc;
   a.status = c->d_status;
   a.trace = c->d_trace;
-  ZD_CUDA(c, zdraw::launch_attn_fwd(stream, tm_q, tm_k, tm_v, a));
+  ZD_CUDA(c, zdraw::launch_attn_fwd(stream, tm_q, tm_k, tm_v, tm_o, a));
   return ZDRAW_CUDA_OK;
 }
 

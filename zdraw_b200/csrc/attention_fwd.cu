@@ -153,7 +153,8 @@ __device__ __forceinline__ void store_row_chunk(const AttnArgs& a, size_t row_of
 template <bool kTrace>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const AttnArgs a) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                const AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -525,18 +526,52 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const size_t row_off = static_cast<size_t>(img) * a.o_batch_stride +
                              static_cast<size_t>(tok) * a.o_tok_stride +
                              static_cast<size_t>(head) * a.o_head_stride;
+      if (a.o_tma && n_act > 0) {
+        // The tile's Q block is free (O complete means every MMA that read it is done): the
+        // normalised rows go there as f16 in the 128-byte swizzle and leave as two 128 x 64 tile
+        // stores, which write whole lines instead of 32 row fragments per store instruction.
+        // Rows past the end of the sequence are clipped by the tensor map.
+        uint8_t* qblk = sbase + kOffQ + t * kTileBytes;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t o[32];
-        if (n_act > 0) {
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t o[32];
           tmem_ld_x32(t_o + 32u * ch, o);
           tmem_wait_ld();
-        }
-        if (tok < a.tokens) {
-          float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = (n_act > 0) ? __uint_as_float(o[i]) * inv_l : 0.0f;
-          store_row_chunk(a, row_off, 32 * ch, v);
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack_f16x2(__uint_as_float(o[8 * i + 0]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l);
+            w.y = pack_f16x2(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
+            w.z = pack_f16x2(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
+            w.w = pack_f16x2(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
+            const int j = 4 * ch + i;  // 16-byte piece of the 256-byte row: block j / 8, piece j % 8
+            *reinterpret_cast<uint4*>(qblk + (j >> 3) * kHalfBytes + row * 128 + (((j & 7) ^ (row & 7)) << 4)) = w;
+          }
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1u + static_cast<uint32_t>(t), 128);
+        if (row == 0) {
+          const int tok0 = (q_tile0 + t) * kBM;
+          const uint32_t src = base + kOffQ + t * kTileBytes;
+          tma_store_4d(&tm_o, src, 0, c1(a.o_head_major, tok0), c2(a.o_head_major, tok0), img);
+          tma_store_4d(&tm_o, src + kHalfBytes, 64, c1(a.o_head_major, tok0), c2(a.o_head_major, tok0), img);
+          bulk_commit_group();
+          bulk_wait_group_read<0>();  // the block must outlive the reads of the copy engine
+        }
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t o[32];
+          if (n_act > 0) {
+            tmem_ld_x32(t_o + 32u * ch, o);
+            tmem_wait_ld();
+          }
+          if (tok < a.tokens) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = (n_act > 0) ? __uint_as_float(o[i]) * inv_l : 0.0f;
+            store_row_chunk(a, row_off, 32 * ch, v);
+          }
         }
       }
     }
@@ -651,7 +686,7 @@ cudaError_t attn_fwd_configure() {
 }
 
 cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
-                            const CUtensorMap& tm_v, const AttnArgs& args) {
+                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args) {
   const int n_q_tiles = (args.tokens + kBM - 1) / kBM;
   dim3 grid((n_q_tiles + 1) / 2, args.heads, args.batch);
   // Programmatic dependent launch: the kernel may become resident while the preceding kernel in
@@ -666,8 +701,8 @@ cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (args.trace != nullptr) return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<true>, tm_q, tm_k, tm_v, args);
-  return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<false>, tm_q, tm_k, tm_v, args);
+  if (args.trace != nullptr) return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<true>, tm_q, tm_k, tm_v, tm_o, args);
+  return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<false>, tm_q, tm_k, tm_v, tm_o, args);
 }
 
 cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args) {

@@ -32,6 +32,10 @@ struct AttnArgs {
   long long tile_list_stride;  // ints between images
   void* o;
   long long o_tok_stride, o_head_stride, o_batch_stride;  // elements
+  // 1: o is f16 and the launch carries a tensor map of it (same shape rules as q): the epilogue
+  // stores 128 x 64 blocks as tiles. 0: rows are stored from registers. o_head_major names the
+  // order of the map's middle coordinates.
+  int o_tma, o_head_major;
   uint32_t* status;  // device status word
   unsigned long long* trace;  // nullptr, or attn_fwd_trace_words() words for pipeline time stamps (debugging)
 };
@@ -53,7 +57,7 @@ int attn_fwd_smem_bytes();
 int attn_fwd_trace_words();
 cudaError_t attn_fwd_configure();  // raises the kernel's dynamic shared-memory limit (once per device)
 cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
-                            const CUtensorMap& tm_v, const AttnArgs& args);
+                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args);
 cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args);
 // Classifies the K/V tiles of each image under `key_mask` and writes the tile lists
 // (1 + n_kv_tiles ints per image, `list_stride` ints apart).

@@ -139,11 +139,20 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int
                "r"(x), "r"(y)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tmap),
+               "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until at most kPending of this thread's bulk groups have not finished READING shared memory.
 template <int kPending>
 __device__ __forceinline__ void bulk_wait_group_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+// Barrier among `threads` threads of the CTA (a multiple of 32) that all name the same id (1..15).
+__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 // Wait until at most kPending of this thread's bulk groups are incomplete (writes performed).
 template <int kPending>
