@@ -315,6 +315,7 @@ def main():
     # ---- the projection GEMM either side of attention (Q projection with the prologue as its
     #      epilogue; a plain f16 projection such as V or the output projection), same token count
     projection = None
+    block = None
     hidden = w.heads * 128
     if not by_heads and hidden % 256 == 0:
         from zdraw_b200._lib import LinearParams
@@ -367,6 +368,28 @@ def main():
             "cublas_f16": {"ms_per_launch": ms_gl, "achieved": gemm_flops / ms_gl / 1e9, "unit": "TFLOP/s",
                            "note": "torch.matmul on the same operands, no epilogue; for comparison only"},
         }
+        # The attention sub-block of a DiT block end to end on the device: q/k/v projection (one
+        # launch, prologue as epilogue) -> attention -> output projection, five weight matrices.
+        block = None
+        if g_sets >= 4 and w.dtype == "f16":
+            blk_o = torch.empty((w.batch, w.tokens, w.heads, 128), dtype=torch.float16, device="cuda")
+            p_blk = workloads.params(w)  # f16, q/k head-major from the projection, v and o token-major
+
+            def block_step(i):
+                j = i % g_sets
+                ctx.qkv_projection(acts[j], wts[j], wts[(j + 1) % g_sets], wts[(j + 2) % g_sets], c_qk[0], c_qk[1],
+                                   c_plain[0], x0["q_w_txt"], x0["q_w_img"], x0["k_w_txt"], x0["k_w_img"],
+                                   x0["rope_cos"], x0["rope_sin"], lp_qk, stream=stream)
+                ctx.run_on_handles(c_qk[0], c_qk[1], c_plain[0].view(w.batch, w.tokens, w.heads, 128), blk_o, p_blk,
+                                   key_mask=x0["key_mask"], stream=stream)
+                ctx.linear(blk_o.view(m_rows, hidden), wts[(j + 3) % g_sets], c_plain[1], lp_plain, stream=stream)
+
+            ms_blk = timed(block_step)
+            blk_flops = 4 * gemm_flops + w.flops
+            block = {"ms_per_step": ms_blk, "achieved": blk_flops / ms_blk / 1e9, "unit": "TFLOP/s",
+                     "flops": blk_flops, "launches_per_step": 3 + (1 if w.masked_text is not None else 0),
+                     "what": "zdraw_cuda_qkv_projection + zdraw_cuda_attention + zdraw_cuda_linear (output projection)"}
+            del blk_o
         del acts, wts, c_plain, c_qk
         if ctx.last_status() != 0:
             raise SystemExit("the projection kernel reported a non-zero status")
@@ -477,6 +500,9 @@ def main():
                     projection[leg]["frac"] = projection[leg]["achieved"] / peaks["bf16_tflops"]
             projection["peak"] = peaks["bf16_tflops"]
             line["projection"] = projection
+            if block is not None:
+                block["frac"] = block["achieved"] / peaks["bf16_tflops"]
+                line["attention_block"] = block
         if wide is not None:
             wide["frac"] = wide["achieved"] / peaks["bf16_tflops"]
             line["wide_attention"] = wide
