@@ -189,6 +189,8 @@ pub extern fn zdraw_cuda_joint_attention_static(
     params: *const AttnParams,
     error_text: ?*[*:0]const u8,
 ) c_int;
+// Debugging: pipeline clock stamps of one CTA into a device buffer of >= 1600 u64 words (null = off).
+pub extern fn zdraw_cuda_attn_set_trace(ctx: *anyopaque, device_words: ?*anyopaque, n_words: usize) c_int;
 pub extern fn zdraw_cuda_last_status(ctx: *anyopaque, stream: ?*anyopaque, status: *u32) c_int;
 pub extern fn zdraw_cuda_last_error(ctx: ?*anyopaque) [*:0]const u8;
 pub extern fn zdraw_cuda_klein_rope_table(
