@@ -65,8 +65,10 @@ __device__ __forceinline__ uint32_t pack_clamped(float lo, float hi) {
 template <typename TIn>
 __global__ void __launch_bounds__(kGroupsPerBlock * 16, 3)
 qk_norm_rope_kernel(const PrologueArgs a, int n_chunks) {
-  // The attention kernel that follows may start its preamble (barriers, TMEM) now; it waits for
-  // this grid to finish before it reads q/k.
+  // The kernel before this one in the stream (it may still be reading the buffers this one
+  // writes) must have finished; the attention kernel that follows may start its preamble
+  // (barriers, TMEM) now: it waits for this grid to finish before it reads q/k.
+  grid_dependency_wait();
   grid_launch_dependents();
   const long long groups = static_cast<long long>(a.batch) * a.tokens * 2 * n_chunks;
   const long long g_raw = static_cast<long long>(blockIdx.x) * kGroupsPerBlock + (threadIdx.x >> 4);
@@ -169,12 +171,20 @@ cudaError_t launch_qk_norm_rope(cudaStream_t stream, const PrologueArgs& a, bool
   const int n_chunks = (a.heads + kHeadsPerGroup - 1) / kHeadsPerGroup;
   const long long groups = static_cast<long long>(a.batch) * a.tokens * 2 * n_chunks;
   const unsigned grid = static_cast<unsigned>((groups + kGroupsPerBlock - 1) / kGroupsPerBlock);
-  if (in_f32) {
-    qk_norm_rope_kernel<float><<<grid, kGroupsPerBlock * 16, 0, stream>>>(a, n_chunks);
-  } else {
-    qk_norm_rope_kernel<__half><<<grid, kGroupsPerBlock * 16, 0, stream>>>(a, n_chunks);
-  }
-  return cudaGetLastError();
+  // Programmatic dependent launch: the grid may be set up while the kernel before it in the stream
+  // drains; the kernel waits for that kernel to finish before it touches memory.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGroupsPerBlock * 16);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (in_f32) return cudaLaunchKernelEx(&cfg, qk_norm_rope_kernel<float>, a, n_chunks);
+  return cudaLaunchKernelEx(&cfg, qk_norm_rope_kernel<__half>, a, n_chunks);
 }
 
 cudaError_t launch_cast_f32_to_f16(cudaStream_t stream, const float* src, void* dst, long long rows,
