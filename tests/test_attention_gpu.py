@@ -234,6 +234,51 @@ def test_joint_host_call_in_head_chunks_matches_device_call(ctx, out_layout):
     assert np.isfinite(out_h.astype(np.float32)).all()
 
 
+def test_joint_call_replays_from_a_cuda_graph(ctx):
+    """With scratch reserved up front the joint call enqueues kernels only, so it can be captured
+    into a CUDA graph once and replayed: the replay gives the bytes of the eager call, and follows
+    the inputs when they change in place."""
+    w = workloads.Workload("graph_case", "klein", 2, 3, 64, 16, 24, seed=17)  # S = 448, two images
+    x = workloads.make_inputs(w, "cuda")
+    p = workloads.params(w)
+    ctx.reserve(p)
+    args = (x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"])
+    eager = torch.empty((w.batch, w.tokens, w.heads, 128), dtype=torch.float16, device="cuda")
+    ctx.joint_attention(*args, eager, p)
+    torch.cuda.synchronize()
+    replayed = torch.zeros_like(eager)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        ctx.joint_attention(*args, replayed, p)  # the wrapper enqueues on the current (capturing) stream
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(replayed, eager)
+    x["v"].mul_(0.5)  # in place: the graph reads the same buffers
+    ctx.joint_attention(*args, eager, p)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(replayed, eager)
+    assert ctx.last_status() == 0
+
+
+def test_packed_qkv_operand_through_strides(ctx):
+    """q, k and v as column blocks of one [tokens][3 * heads * 128] tensor (what a fused QKV
+    projection leaves): pointer offsets and a common row stride, no repacking."""
+    w = workloads.Workload("packed_qkv", "klein", 1, 4, 32, 10, 13, seed=23)  # S = 162
+    x = workloads.make_inputs(w, "cuda")
+    hd = w.heads * 128
+    packed = torch.cat([x[n].reshape(w.tokens, hd) for n in ("q", "k", "v")], dim=1).contiguous()
+    small = (x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"])
+    want = torch.empty((1, w.tokens, w.heads, 128), dtype=torch.float16, device="cuda")
+    ctx.joint_attention(x["q"], x["k"], x["v"], *small, want, workloads.params(w))
+    got = torch.empty_like(want)
+    p = workloads.params(w, ld_q=3 * hd, ld_k=3 * hd, ld_v=3 * hd)
+    ctx.joint_attention(packed[:, :hd], packed[:, hd:2 * hd], packed[:, 2 * hd:], *small, got, p)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+
+
 def test_pipeline_trace_facility(ctx):
     """zdraw_cuda_attn_set_trace: the instrumented kernel gives the same bytes and monotonic stamps."""
     import ctypes as C
