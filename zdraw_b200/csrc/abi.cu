@@ -1,63 +1,18 @@
-// extern "C" shim of the joint-attention path: argument validation, context scratch,
+// extern "C" shim of the joint-attention path: contexts, argument validation, context scratch,
 // tensor-map construction and kernel launches. See include/zdraw_cuda.h for the contract
-// and for the reference entry points each function replaces.
-#include <cuda.h>
-#include <cuda_runtime.h>
-
+// and for the reference entry points each function replaces. The projections and the wide
+// attention are in abi_linear.cu, the RoPE tables in abi_tables.cu.
 #include <cmath>
-#include <cstdarg>
-#include <cstdint>
-#include <cstdio>
 #include <cstring>
 #include <new>
 
-#include "../../include/zdraw_cuda.h"
+#include "abi_internal.cuh"
 #include "attention_fwd.cuh"
 #include "linear.cuh"
-#include "rope_table.cuh"
-#include "wide_attention.cuh"
 #include "prologue.cuh"
 
-namespace {
-
-using zdraw::AttnArgs;
-using zdraw::PrologueArgs;
-using zdraw::ScalarArgs;
-
-constexpr int kHeadDim = 128;
-constexpr uint32_t kMaxTokens = 1u << 20;
-constexpr float kLog2e = 1.4426950408889634f;
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-struct Buf {
-  void* p = nullptr;
-  size_t cap = 0;
-};
-
-struct Ctx {
-  uint32_t magic = 0x5a444154u;  // "ZDAT"
-  int device = 0;
-  uint32_t* d_status = nullptr;
-  EncodeTiledFn encode = nullptr;
-  int sm_count = 0;
-  cudaStream_t host_stream = nullptr;  // kernels of the host-buffer entry points
-  // Host-buffer joint call: copies in and out run on their own streams, one event pair per head
-  // chunk, so the PCIe transfers of one chunk overlap the kernels and the transfers of others.
-  cudaStream_t in_stream = nullptr, out_stream = nullptr;
-  static constexpr int kMaxChunks = 16;
-  cudaEvent_t ev_in[kMaxChunks] = {}, ev_done[kMaxChunks] = {};
-  unsigned long long* d_trace = nullptr;  // caller's trace buffer while pipeline tracing is on (debugging)
-  // Grow-only scratch (device memory).
-  Buf q16, k16, v16, tile_list;
-  Buf st_q, st_k, st_v, st_o, st_w, st_cos, st_sin, st_mask;  // staging for the host-buffer path
-  Buf wa_q16, wa_k16, wa_vt16, wa_aux, wa_p;  // wide-head attention: half operands, row statistics, exp(scores)
-  Buf wa_q8, wa_k8;                            // e4m3 copies of Q and K for the row-max pass
-  char err[256] = {0};
-};
+namespace zdraw {
+namespace abi {
 
 int fail(Ctx* c, int code, const char* fmt, ...) {
   if (c) {
@@ -67,17 +22,6 @@ int fail(Ctx* c, int code, const char* fmt, ...) {
     va_end(ap);
   }
   return code;
-}
-
-#define ZD_CUDA(c, expr)                                                                      \
-  do {                                                                                        \
-    cudaError_t e_ = (expr);                                                                  \
-    if (e_ != cudaSuccess) return fail((c), ZDRAW_CUDA_E_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
-  } while (0)
-
-Ctx* as_ctx(void* p) {
-  Ctx* c = static_cast<Ctx*>(p);
-  return (c && c->magic == 0x5a444154u) ? c : nullptr;
 }
 
 int ensure(Ctx* c, Buf& b, size_t bytes) {
@@ -92,9 +36,15 @@ int ensure(Ctx* c, Buf& b, size_t bytes) {
   return ZDRAW_CUDA_OK;
 }
 
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+}  // namespace abi
+}  // namespace zdraw
 
-size_t dtype_size(uint32_t dt) { return dt == ZDRAW_DTYPE_F32 ? 4 : 2; }
+namespace {
+
+using namespace zdraw::abi;
+using zdraw::AttnArgs;
+using zdraw::PrologueArgs;
+using zdraw::ScalarArgs;
 
 // Resolved, validated view of the params.
 struct Shape {
@@ -630,217 +580,7 @@ int zdraw_cuda_last_status(void* ctx, void* stream, uint32_t* device_status) {
 
 }  // extern "C"
 
-namespace {
-
-// One product of a projection launch as the entry points describe it.
-struct PartSpec {
-  const void* w;
-  void* c;
-  uint32_t epilogue;  // zdraw::kEpilogue*: 0 plain, 1 qk; 2 row max and 3 exp are internal (wide attention)
-  const float *w_txt, *w_img;
-  const float* row_scale = nullptr;  // plain: optional factor per row
-  unsigned int* row_key = nullptr;   // row max / exp: ordered keys of the row maxima
-  float* row_sum = nullptr;          // exp: partial row sums
-  float exp_scale = 0.0f;
-};
-
-// Shared body of zdraw_cuda_linear and zdraw_cuda_qkv_projection: validates, builds the tensor
-// maps and launches one kernel that computes every part from the same A.
-// operands_e4m3 (internal, the row-max pass of the wide attention): A and W hold e4m3 bytes instead
-// of halves; p->a_dtype / w_dtype still say f16 and strides count elements.
-int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec* parts, const float* rope_cos,
-               const float* rope_sin, const zdraw_cuda_linear_params* p, bool operands_e4m3 = false) {
-  if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
-  if (p->reserved != 0 || p->m == 0 || p->n == 0 || p->k == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero size or reserved != 0");
-  if (p->c_dtype != ZDRAW_DTYPE_F16 && p->c_dtype != ZDRAW_DTYPE_F32) return fail(cx, ZDRAW_CUDA_E_ARG, "bad c_dtype");
-  if (!a || !aligned16(a)) return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned matrix");
-  bool any_qk = false;
-  for (int i = 0; i < n_parts; ++i) {
-    if (parts[i].epilogue > 3) return fail(cx, ZDRAW_CUDA_E_ARG, "bad epilogue");
-    if (!parts[i].w || !parts[i].c || !aligned16(parts[i].w) || !aligned16(parts[i].c))
-      return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned matrix");
-    any_qk = any_qk || parts[i].epilogue == 1;
-  }
-  // Shapes and types outside the kernel: declined, nothing enqueued (the reference's fast GEMMs
-  // admit 32-aligned dims only, src/metal/mres_util.zig:30-38).
-  if (p->a_dtype != ZDRAW_DTYPE_F16 || p->w_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_DECLINED, "A and W must be f16");
-  if (p->n % 256 != 0 || p->k % 64 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "n must be a multiple of 256 and k of 64");
-  if (operands_e4m3 && p->k % 128 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "k must be a multiple of 128 for 8-bit operands");
-  if (p->m > (1u << 30) || p->n > (1u << 30) || p->k > (1u << 30)) return fail(cx, ZDRAW_CUDA_DECLINED, "shape too large");
-  const long long ld_a = p->ld_a ? static_cast<long long>(p->ld_a) : p->k;
-  const long long ld_w = p->ld_w ? static_cast<long long>(p->ld_w) : p->k;
-  const long long ld_c = p->ld_c ? static_cast<long long>(p->ld_c) : p->n;
-  if (ld_a < p->k || ld_w < p->k || ld_c < p->n) return fail(cx, ZDRAW_CUDA_E_ARG, "row stride smaller than the row");
-  const long long ld_align = operands_e4m3 ? 16 : 8;  // TMA strides are multiples of 16 bytes
-  if (ld_a % ld_align != 0 || ld_w % ld_align != 0 || ld_c % 8 != 0)
-    return fail(cx, ZDRAW_CUDA_DECLINED, "row strides must be multiples of 8 elements (16 for 8-bit operands)");
-  zdraw::LinearArgs la = {};
-  la.m = static_cast<int>(p->m);
-  la.n = static_cast<int>(p->n);
-  la.k = static_cast<int>(p->k);
-  la.fp8 = operands_e4m3 ? 1 : 0;
-  la.n_parts = n_parts;
-  la.status = cx->d_status;
-  if (any_qk) {
-    if (p->tokens == 0 || p->heads == 0 || p->m % p->tokens != 0 || p->n != p->heads * 128u || p->txt_tokens > p->tokens)
-      return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs m = images * tokens and n = heads * 128");
-    if (!rope_cos || !rope_sin || !aligned16(rope_cos) || !aligned16(rope_sin) || p->rope_batch_stride % 4 != 0)
-      return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs aligned tables");
-    if (!(p->norm_eps >= 0.0f)) return fail(cx, ZDRAW_CUDA_E_ARG, "norm_eps must be >= 0");
-    la.tokens = static_cast<int>(p->tokens);
-    la.heads = static_cast<int>(p->heads);
-    la.txt_tokens = static_cast<int>(p->txt_tokens);
-    la.norm_eps = p->norm_eps;
-    la.rope_cos = rope_cos;
-    la.rope_sin = rope_sin;
-    la.rope_batch_stride = static_cast<long long>(p->rope_batch_stride);
-  }
-  for (int i = 0; i < n_parts; ++i) {
-    zdraw::LinearPart& lp = la.part[i];
-    lp.epilogue = static_cast<int>(parts[i].epilogue);
-    lp.c = parts[i].c;
-    if (parts[i].epilogue == 1) {
-      if (!parts[i].w_txt || !parts[i].w_img || !aligned16(parts[i].w_txt) || !aligned16(parts[i].w_img))
-        return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs aligned norm weights");
-      lp.w_txt = parts[i].w_txt;
-      lp.w_img = parts[i].w_img;
-    } else {
-      lp.c_f32 = p->c_dtype == ZDRAW_DTYPE_F32;
-      lp.ld_c = ld_c;
-      lp.row_scale = parts[i].row_scale;
-      lp.row_key = parts[i].row_key;
-      lp.row_sum = parts[i].row_sum;
-      lp.exp_scale = parts[i].exp_scale;
-    }
-  }
-  ZD_CUDA(cx, cudaSetDevice(cx->device));
-  // Row-major matrices [rows][ld] as tiled tensor maps: boxes of 128 bytes (64 halves) x 128 rows.
-  zdraw::LinearMaps maps;
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const cuuint64_t esz = operands_e4m3 ? 1u : 2u;
-  auto encode = [&](CUtensorMap* tm, const void* base_ptr, uint64_t rows, long long ld) {
-    const cuuint64_t dims[4] = {p->k, rows, 1, 1};
-    const cuuint64_t strides[3] = {esz * static_cast<cuuint64_t>(ld), esz * static_cast<cuuint64_t>(ld) * rows,
-                                   esz * static_cast<cuuint64_t>(ld) * rows};
-    const cuuint32_t box[4] = {operands_e4m3 ? 128u : 64u, 128, 1, 1};  // 128-byte rows either way
-    return cx->encode(tm, operands_e4m3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                      const_cast<void*>(base_ptr), dims, strides, box, estr,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  };
-  if (encode(&maps.a, a, p->m, ld_a) != CUDA_SUCCESS) return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
-  for (int i = 0; i < zdraw::kMaxLinearParts; ++i)
-    if (encode(&maps.w[i], parts[i < n_parts ? i : 0].w, p->n, ld_w) != CUDA_SUCCESS)
-      return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
-  // Plain parts: C for the epilogue's tile stores (32 columns x 32 rows, swizzle of the row size).
-  for (int i = 0; i < zdraw::kMaxLinearParts; ++i) {
-    maps.c[i] = maps.a;  // any valid map where none is used
-    if (i >= n_parts || (parts[i].epilogue != 0 && parts[i].epilogue != 3)) continue;
-    const bool f32 = p->c_dtype == ZDRAW_DTYPE_F32;
-    const cuuint64_t dims[2] = {p->n, p->m};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_c) * (f32 ? 4u : 2u)};
-    const cuuint32_t box[2] = {32u, 32u};  // 128-byte rows of f32, 64-byte rows of f16
-    const cuuint32_t es[2] = {1, 1};
-    if (cx->encode(&maps.c[i], f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, parts[i].c, dims,
-                   strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed for C");
-  }
-  ZD_CUDA(cx, zdraw::launch_linear(static_cast<cudaStream_t>(stream), maps, la, cx->sm_count));
-  return ZDRAW_CUDA_OK;
-}
-
-}  // namespace
-
 extern "C" {
-
-int zdraw_cuda_linear(void* ctx, void* stream, const void* a, const void* w, void* c, const float* norm_w_txt,
-                      const float* norm_w_img, const float* rope_cos, const float* rope_sin,
-                      const zdraw_cuda_linear_params* p) {
-  Ctx* cx = as_ctx(ctx);
-  if (!cx) return ZDRAW_CUDA_E_ARG;
-  if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
-  if (p->epilogue > 1) return fail(cx, ZDRAW_CUDA_E_ARG, "bad epilogue");
-  if (p->epilogue == 1 && p->c_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_E_ARG, "the qk epilogue writes f16");
-  const PartSpec part = {w, c, p->epilogue, norm_w_txt, norm_w_img};
-  return run_linear(cx, stream, a, 1, &part, rope_cos, rope_sin, p);
-}
-
-int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const float* k, const float* v, float* o,
-                              size_t tokens, size_t head_dim) {
-  Ctx* cx = as_ctx(ctx);
-  if (!cx) return ZDRAW_CUDA_E_ARG;
-  if (!q || !k || !v || !o || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
-    return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned tensor");
-  if (tokens == 0 || head_dim == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero tokens or head_dim");
-  // Shapes outside the kernels are declined (the reference's own admission is tokens % 32 and
-  // head_dim % 32, src/metal/mvattn_owned.zig:271-272): both products run on the 256-column tiles
-  // of the projection kernel; the token bound keeps the tokens^2 half scratch below 9 GB.
-  if (tokens % 256 != 0 || head_dim % 256 != 0 || tokens > 65536 || head_dim > 4096)
-    return fail(cx, ZDRAW_CUDA_DECLINED, "tokens and head_dim must be multiples of 256, tokens <= 65536");
-  ZD_CUDA(cx, cudaSetDevice(cx->device));
-  const size_t n = tokens * head_dim;
-  const size_t n_partial = 2 * (tokens / 256);  // partial row sums: one per 128-column half tile
-  const size_t aux_bytes = tokens * 4 * (2 + n_partial);  // row keys, 1/row sum, partial sums
-  int rc;
-  if ((rc = ensure(cx, cx->wa_q16, n * 2)) || (rc = ensure(cx, cx->wa_k16, n * 2)) || (rc = ensure(cx, cx->wa_vt16, n * 2)) ||
-      (rc = ensure(cx, cx->wa_aux, aux_bytes)) || (rc = ensure(cx, cx->wa_p, tokens * tokens * 2)) ||
-      (rc = ensure(cx, cx->wa_q8, n)) || (rc = ensure(cx, cx->wa_k8, n)))
-    return rc;
-  unsigned int* row_key = static_cast<unsigned int*>(cx->wa_aux.p);
-  float* row_inv = reinterpret_cast<float*>(row_key + tokens);
-  float* row_sum = row_inv + tokens;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // kf32_to_h x2, kvt_transpose_h (mvattn_owned.zig:322-330); Q and K also as e4m3 (see below)
-  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16_e4m3(st, q, cx->wa_q16.p, cx->wa_q8.p, static_cast<long long>(n)));
-  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16_e4m3(st, k, cx->wa_k16.p, cx->wa_k8.p, static_cast<long long>(n)));
-  ZD_CUDA(cx, zdraw::launch_transpose_cast(st, v, cx->wa_vt16.p, static_cast<int>(tokens), static_cast<int>(head_dim)));
-  ZD_CUDA(cx, cudaMemsetAsync(row_key, 0, tokens * 4, st));  // key 0 lies below every float
-  // The scores S = Q K^T (K is already [n][k]) are never stored. A first product keeps only each
-  // row's maximum; a second one turns its accumulator into exp(scale (S - max)) in half and keeps
-  // partial row sums: recomputing S (k = head_dim is short) costs less than writing and re-reading
-  // tokens^2 f32 scores. Softmax does not change when another number than the exact maximum is
-  // subtracted, as long as nothing overflows, so the first product runs on e4m3 copies of Q and K
-  // at twice the rate: its maxima are a few percent of |S| off, and the exponentials are clamped
-  // to the half range.
-  zdraw_cuda_linear_params ps = {};
-  ps.m = static_cast<uint32_t>(tokens);
-  ps.n = static_cast<uint32_t>(tokens);
-  ps.k = static_cast<uint32_t>(head_dim);
-  ps.a_dtype = ps.w_dtype = ps.c_dtype = ZDRAW_DTYPE_F16;
-  PartSpec part_s = {cx->wa_k16.p, cx->wa_p.p, static_cast<uint32_t>(zdraw::kEpilogueRowMax), nullptr, nullptr};
-  part_s.row_key = row_key;
-  part_s.w = cx->wa_k8.p;
-  if ((rc = run_linear(cx, stream, cx->wa_q8.p, 1, &part_s, nullptr, nullptr, &ps, true)) != 0) return rc;
-  part_s.w = cx->wa_k16.p;
-  part_s.epilogue = static_cast<uint32_t>(zdraw::kEpilogueExp);
-  part_s.row_sum = row_sum;
-  part_s.exp_scale = 1.4426950408889634f / std::sqrt(static_cast<float>(head_dim));
-  if ((rc = run_linear(cx, stream, cx->wa_q16.p, 1, &part_s, nullptr, nullptr, &ps)) != 0) return rc;
-  ZD_CUDA(cx, zdraw::launch_row_sum_inverse(st, row_sum, static_cast<int>(n_partial), static_cast<long long>(tokens), row_inv));
-  // O[tokens, head_dim] = (P (V^T)^T) / row sum, f32 out
-  zdraw_cuda_linear_params po = {};
-  po.m = static_cast<uint32_t>(tokens);
-  po.n = static_cast<uint32_t>(head_dim);
-  po.k = static_cast<uint32_t>(tokens);
-  po.a_dtype = po.w_dtype = ZDRAW_DTYPE_F16;
-  po.c_dtype = ZDRAW_DTYPE_F32;
-  PartSpec part_o = {cx->wa_vt16.p, o, 0, nullptr, nullptr};
-  part_o.row_scale = row_inv;
-  return run_linear(cx, stream, cx->wa_p.p, 1, &part_o, nullptr, nullptr, &po);
-}
-
-int zdraw_cuda_qkv_projection(void* ctx, void* stream, const void* x, const void* wq, const void* wk, const void* wv,
-                              void* q16, void* k16, void* v, const float* q_w_txt, const float* q_w_img,
-                              const float* k_w_txt, const float* k_w_img, const float* rope_cos,
-                              const float* rope_sin, const zdraw_cuda_linear_params* p) {
-  Ctx* cx = as_ctx(ctx);
-  if (!cx) return ZDRAW_CUDA_E_ARG;
-  if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
-  if (p->epilogue != 1) return fail(cx, ZDRAW_CUDA_E_ARG, "the q/k/v projection takes epilogue = 1 (q and k get the prologue)");
-  const PartSpec parts[3] = {{wq, q16, 1, q_w_txt, q_w_img}, {wk, k16, 1, k_w_txt, k_w_img}, {wv, v, 0, nullptr, nullptr}};
-  return run_linear(cx, stream, x, 3, parts, rope_cos, rope_sin, p);
-}
 
 int zdraw_cuda_attn_set_trace(void* ctx, void* device_words, size_t n_words) {
   Ctx* c = as_ctx(ctx);
@@ -857,146 +597,5 @@ const char* zdraw_cuda_last_error(void* ctx) {
 }
 
 // --------------------------------------------------------------------------- host-side RoPE tables
-
-int zdraw_cuda_klein_rope_table(float* cos_out, float* sin_out, size_t txt_len, size_t grid_h, size_t grid_w,
-                                size_t ref_h, size_t ref_w, double theta) {
-  if (!cos_out || !sin_out || !(theta > 0.0)) return ZDRAW_CUDA_E_ARG;
-  if ((grid_h == 0) != (grid_w == 0) || (ref_h == 0) != (ref_w == 0)) return ZDRAW_CUDA_E_ARG;
-  // 16 frequencies per 32-wide axis, shared by the four axes.
-  double freq[16];
-  for (int i = 0; i < 16; ++i) freq[i] = 1.0 / std::pow(theta, static_cast<double>(2 * i) / 32.0);
-  const size_t img = grid_h * grid_w;
-  const size_t total = txt_len + img + ref_h * ref_w;
-  for (size_t t = 0; t < total; ++t) {
-    double id[4] = {0.0, 0.0, 0.0, 0.0};  // (T, H, W, L)
-    if (t < txt_len) {
-      id[3] = static_cast<double>(t);
-    } else if (t < txt_len + img) {
-      id[1] = static_cast<double>((t - txt_len) / grid_w);
-      id[2] = static_cast<double>((t - txt_len) % grid_w);
-    } else {
-      id[0] = 10.0;
-      id[1] = static_cast<double>((t - txt_len - img) / ref_w);
-      id[2] = static_cast<double>((t - txt_len - img) % ref_w);
-    }
-    float* c = cos_out + t * kHeadDim;
-    float* s = sin_out + t * kHeadDim;
-    for (int ax = 0; ax < 4; ++ax)
-      for (int i = 0; i < 16; ++i) {
-        const double ang = id[ax] * freq[i];
-        c[ax * 32 + 2 * i] = c[ax * 32 + 2 * i + 1] = static_cast<float>(std::cos(ang));
-        s[ax * 32 + 2 * i] = s[ax * 32 + 2 * i + 1] = static_cast<float>(std::sin(ang));
-      }
-  }
-  return ZDRAW_CUDA_OK;
-}
-
-int zdraw_cuda_zimage_rope_table(float* cos_out, float* sin_out, size_t img_h, size_t img_w, size_t cap_total,
-                                 const size_t dims[3], const size_t lens[3], float theta) {
-  if (!cos_out || !sin_out || !dims || !lens) return ZDRAW_CUDA_E_ARG;
-  if (!(theta > 0.0f)) return ZDRAW_CUDA_E_ARG;
-  size_t width = 0;
-  for (int a = 0; a < 3; ++a) {
-    if (dims[a] == 0 || lens[a] == 0 || dims[a] % 2 != 0) return ZDRAW_CUDA_E_ARG;
-    width += dims[a];
-  }
-  if (width != kHeadDim) return ZDRAW_CUDA_E_ARG;
-  const size_t n_img = img_h * img_w;
-  const float neg_log_theta = -std::log(theta);
-  for (size_t t = 0; t < n_img + cap_total; ++t) {
-    size_t pos[3];
-    if (t < n_img) {  // image tokens come first
-      pos[0] = cap_total + 1;
-      pos[1] = t / img_w;
-      pos[2] = t % img_w;
-    } else {
-      pos[0] = 1 + (t - n_img);
-      pos[1] = 0;
-      pos[2] = 0;
-    }
-    size_t col = 0;
-    for (int a = 0; a < 3; ++a) {
-      if (pos[a] >= lens[a]) return ZDRAW_CUDA_E_ARG;  // BadPosition
-      const float fpos = static_cast<float>(pos[a]);
-      for (size_t pr = 0; pr < dims[a] / 2; ++pr) {
-        const float power = 2.0f * static_cast<float>(pr) / static_cast<float>(dims[a]);
-        const float ang = fpos * std::exp(neg_log_theta * power);
-        const size_t o = t * kHeadDim + col + 2 * pr;
-        cos_out[o] = cos_out[o + 1] = std::cos(ang);
-        sin_out[o] = sin_out[o + 1] = std::sin(ang);
-      }
-      col += dims[a];
-    }
-  }
-  return ZDRAW_CUDA_OK;
-}
-
-int zdraw_cuda_klein_rope_table_device(void* ctx, void* stream, float* cos_dev, float* sin_dev, size_t txt_len,
-                                       size_t grid_h, size_t grid_w, size_t ref_h, size_t ref_w, double theta) {
-  Ctx* c = as_ctx(ctx);
-  if (!c) return ZDRAW_CUDA_E_ARG;
-  if (!cos_dev || !sin_dev || !aligned16(cos_dev) || !aligned16(sin_dev) || !(theta > 0.0))
-    return fail(c, ZDRAW_CUDA_E_ARG, "null or misaligned table pointer, or theta <= 0");
-  if ((grid_h == 0) != (grid_w == 0) || (ref_h == 0) != (ref_w == 0))
-    return fail(c, ZDRAW_CUDA_E_ARG, "InvalidConfig: a grid needs both sides");
-  const size_t total = txt_len + grid_h * grid_w + ref_h * ref_w;
-  if (txt_len > kMaxTokens || grid_h > kMaxTokens || grid_w > kMaxTokens || ref_h > kMaxTokens || ref_w > kMaxTokens ||
-      total > kMaxTokens)
-    return fail(c, ZDRAW_CUDA_DECLINED, "more tokens than the attention kernels take");
-  zdraw::KleinRopeArgs a = {};
-  a.cos_out = cos_dev;
-  a.sin_out = sin_dev;
-  a.txt_len = static_cast<int>(txt_len);
-  a.grid_h = static_cast<int>(grid_h);
-  a.grid_w = static_cast<int>(grid_w);
-  a.ref_h = static_cast<int>(ref_h);
-  a.ref_w = static_cast<int>(ref_w);
-  a.tokens = static_cast<int>(total);
-  // The host builder's frequencies, bit for bit.
-  for (int i = 0; i < 16; ++i) a.freq[i] = 1.0 / std::pow(theta, static_cast<double>(2 * i) / 32.0);
-  ZD_CUDA(c, cudaSetDevice(c->device));
-  ZD_CUDA(c, zdraw::launch_klein_rope_table(static_cast<cudaStream_t>(stream), a));
-  return ZDRAW_CUDA_OK;
-}
-
-int zdraw_cuda_zimage_rope_table_device(void* ctx, void* stream, float* cos_dev, float* sin_dev, size_t img_h,
-                                        size_t img_w, size_t cap_total, const size_t dims[3], const size_t lens[3],
-                                        float theta) {
-  Ctx* c = as_ctx(ctx);
-  if (!c) return ZDRAW_CUDA_E_ARG;
-  if (!cos_dev || !sin_dev || !aligned16(cos_dev) || !aligned16(sin_dev) || !dims || !lens || !(theta > 0.0f))
-    return fail(c, ZDRAW_CUDA_E_ARG, "null or misaligned pointer, or theta <= 0");
-  size_t width = 0;
-  for (int a = 0; a < 3; ++a) {
-    if (dims[a] == 0 || lens[a] == 0 || dims[a] % 2 != 0) return fail(c, ZDRAW_CUDA_E_ARG, "InvalidConfig: axis sizes");
-    width += dims[a];
-  }
-  if (width != kHeadDim) return fail(c, ZDRAW_CUDA_E_ARG, "InvalidConfig: axis sizes do not add up to 128");
-  if (img_h > kMaxTokens || img_w > kMaxTokens || cap_total > kMaxTokens || img_h * img_w + cap_total > kMaxTokens)
-    return fail(c, ZDRAW_CUDA_DECLINED, "more tokens than the attention kernels take");
-  // BadPosition, as the host builder finds it token by token: the largest position on each axis.
-  const size_t n_img = img_h * img_w;
-  if (n_img > 0 && (cap_total + 1 >= lens[0] || img_h - 1 >= lens[1] || img_w - 1 >= lens[2]))
-    return fail(c, ZDRAW_CUDA_E_ARG, "BadPosition: image position beyond the axis length");
-  if (cap_total > 0 && cap_total >= lens[0]) return fail(c, ZDRAW_CUDA_E_ARG, "BadPosition: caption position beyond the axis length");
-  zdraw::ZimageRopeArgs a = {};
-  a.cos_out = cos_dev;
-  a.sin_out = sin_dev;
-  a.img_h = static_cast<int>(img_h);
-  a.img_w = static_cast<int>(img_w);
-  a.cap_total = static_cast<int>(cap_total);
-  a.tokens = static_cast<int>(n_img + cap_total);
-  const float neg_log_theta = -std::log(theta);
-  int pair = 0;
-  for (int ax = 0; ax < 3; ++ax)
-    for (size_t pr = 0; pr < dims[ax] / 2; ++pr, ++pair) {
-      const float power = 2.0f * static_cast<float>(pr) / static_cast<float>(dims[ax]);
-      a.freq[pair] = std::exp(neg_log_theta * power);  // the host builder's f32 frequency
-      a.axis[pair] = static_cast<unsigned char>(ax);
-    }
-  ZD_CUDA(c, cudaSetDevice(c->device));
-  ZD_CUDA(c, zdraw::launch_zimage_rope_table(static_cast<cudaStream_t>(stream), a));
-  return ZDRAW_CUDA_OK;
-}
 
 }  // extern "C"
