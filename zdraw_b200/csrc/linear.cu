@@ -1,5 +1,5 @@
 // Projection GEMM for the steps either side of attention: C[m, n] = A[m, k] * W[n, k]^T, f16
-// operands, f32 accumulation in TMEM (tcgen05.mma), with two epilogues:
+// operands, f32 accumulation in TMEM (tcgen05.mma), with these epilogues:
 //
 //   plain    C stored as f32 or f16, row-major with stride ld_c — the reference's
 //            gemmRunF16A / gemm_f16_direct for the V projection and the output projection
@@ -8,14 +8,21 @@
 //            per-(token, head) RMSNorm with per-segment weights, pair-rotation RoPE, clamp, fp16,
 //            stored head-major [image][head][token][128] — i.e. the Q and K projections followed
 //            by krms_rope_hm (src/klein/zflux2_glue_shader.zig:95-122) without the f32 q/k
-//            round trip through memory that the reference makes between the two.
+//            round trip through memory that the reference makes between the two;
+//   row max  nothing stored but the maximum of each row (an ordered key updated with atomicMax),
+//   exp      C = half(exp2((A W^T - max[row]) * scale)) plus partial row sums: the two passes of
+//            the wide-head attention's softmax (the reference's krow_softmax_h,
+//            src/metal/mvattn_owned.zig:95-128), so its f32 scores never reach memory.
+//
+// Up to three products that share A run as one launch (the q, k and v projections), and A and W
+// may be e4m3 bytes (the row-max pass, tcgen05 kind::f8f6f4).
 //
 // Persistent, warp-specialised, one CTA pair (cluster of two, tcgen05 cta_group::2) per 256 x 256
 // tile of C: each CTA stages its own 128 rows of A and 128 of the tile's 256 rows of W
 // (128B-swizzled 64-wide K slices, 32 KB per stage, 5 stages, TMA without multicast), the
 // even-rank CTA's warp 1 issues M256 N256 K16 MMAs that read A from each CTA's own shared memory
 // and W from both, and each CTA ends up with its 128 rows x 256 columns of the accumulator in
-// its own TMEM. Pairing halves the bytes each SM pulls from L2 per MMA compared with a lone CTA
+// its own TMEM. Pairing cuts the bytes each SM pulls from L2 per MMA by a third compared with a lone CTA
 // on a 128 x 256 tile, which is what keeps the tensor pipe fed. Warps 4-11 of both CTAs run the
 // epilogue (warps 4-7 columns [0,128), warps 8-11 columns [128,256) of a row) out of one of two
 // 256-column accumulators while the tensor cores fill the other. Tiles are assigned statically
