@@ -189,6 +189,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="klein_1024")
+    ap.add_argument("--batch", type=int, default=0, help="images per GPU (0 = the workload's own batch)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU-baseline sample budget")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -225,6 +226,8 @@ def main():
         torch.cuda.synchronize()
 
     w0 = workloads.WORKLOADS[args.workload]
+    if args.batch > 0:
+        w0 = w0.with_batch(args.batch)
     from dataclasses import replace
 
     from zdraw_b200 import shard as shardlib
