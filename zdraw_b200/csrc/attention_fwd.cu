@@ -5,8 +5,9 @@
 // vendor/mfa/mfa-fwd-d128.metal:408-1541 and src/metal/mattn_block_shader.zig:24-187)
 // with one warp-specialised kernel:
 //
-//   warp 0      TMA producer: Q tiles once, then K_j / V_j tiles through a ring of
-//               128B-swizzled shared-memory stages (cp.async.bulk.tensor, no multicast)
+//   warp 0      TMA producer: Q tiles once, then K and V tiles through a ring of two
+//               128B-swizzled shared-memory slots, a slot holding V of one K/V tile and K of
+//               the next (cp.async.bulk.tensor, no multicast)
 //   warp 1      MMA issuer: tcgen05.mma, S = Q K^T (both operands in shared memory)
 //               and O += P V (P read from tensor memory), accumulators in TMEM
 //   warps 4-7   softmax for query tile 0, one thread per query row
@@ -43,7 +44,8 @@ namespace {
 
 constexpr int kBM = 128;           // query rows per tile
 constexpr int kBN = 128;           // keys per K/V tile
-constexpr int kStages = 4;         // K/V ring depth (one tile per stage)
+constexpr int kStages = 4;         // K/V tiles the ring holds (two per slot)
+constexpr int kPairStages = 2;     // ring slots: a slot holds V of one K/V tile and K of the next
 constexpr int kTileBytes = 32768;  // 128 rows x 128 f16
 constexpr int kHalfBytes = 16384;  // 128 rows x 64 f16: one 128B-swizzled block
 constexpr int kThreads = 384;
@@ -235,23 +237,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tma_load_4d(dst + kHalfBytes, &tm_q, bar(kBarQFull + t), 64, c1(a.q_head_major, row),
                       c2(a.q_head_major, row), img);
         }
-        uint32_t it = 0;
+        // The ring holds pairs: pair i is V of K/V tile i-1 (first 32 KB) and K of tile i (second
+        // 32 KB), which is what one step of the MMA loop consumes (P V of step i-1, Q K^T of step
+        // i) - one barrier to poll and one to release per step. Pair 0 holds K_0 only, the last
+        // pair V of the last tile only.
         bool ok = true;
-        for (int jj = 0; jj < n_act && ok; ++jj) {
-          const int row = (tile_entry(jj) & kTileIndexMask) * kBN;
-          for (int which = 0; which < 2; ++which, ++it) {
-            const uint32_t stage = it % kStages;
-            const uint32_t phase = (it / kStages) & 1u;
-            stamp(3, jj, 2 * which);
-            ok = wait_bar(bar(kBarKVEmpty + stage), phase ^ 1u, abort_flag, a.status, kStProducer);
-            if (!ok) break;
-            stamp(3, jj, 2 * which + 1);
-            const uint32_t dst = base + kOffKV + stage * kTileBytes;
-            const CUtensorMap* tm = which ? &tm_v : &tm_k;
-            const int hm = which ? a.v_head_major : a.k_head_major;
-            mbar_arrive_expect_tx(bar(kBarKVFull + stage), kTileBytes);
-            tma_load_4d(dst, tm, bar(kBarKVFull + stage), 0, c1(hm, row), c2(hm, row), img);
-            tma_load_4d(dst + kHalfBytes, tm, bar(kBarKVFull + stage), 64, c1(hm, row), c2(hm, row), img);
+        for (int i = 0; i <= n_act && ok; ++i) {
+          const uint32_t slot = static_cast<uint32_t>(i) % kPairStages;
+          const uint32_t phase = (static_cast<uint32_t>(i) / kPairStages) & 1u;
+          stamp(3, i, 0);
+          ok = wait_bar(bar(kBarKVEmpty + slot), phase ^ 1u, abort_flag, a.status, kStProducer);
+          if (!ok) break;
+          stamp(3, i, 1);
+          const uint32_t dst = base + kOffKV + slot * 2 * kTileBytes;
+          const bool has_v = i >= 1, has_k = i < n_act;
+          mbar_arrive_expect_tx(bar(kBarKVFull + slot), (has_v ? kTileBytes : 0) + (has_k ? kTileBytes : 0));
+          if (has_v) {
+            const int row = (tile_entry(i - 1) & kTileIndexMask) * kBN;
+            const int hm = a.v_head_major;
+            tma_load_4d(dst, &tm_v, bar(kBarKVFull + slot), 0, c1(hm, row), c2(hm, row), img);
+            tma_load_4d(dst + kHalfBytes, &tm_v, bar(kBarKVFull + slot), 64, c1(hm, row), c2(hm, row), img);
+          }
+          if (has_k) {
+            const int row = (tile_entry(i) & kTileIndexMask) * kBN;
+            const int hm = a.k_head_major;
+            tma_load_4d(dst + kTileBytes, &tm_k, bar(kBarKVFull + slot), 0, c1(hm, row), c2(hm, row), img);
+            tma_load_4d(dst + kTileBytes + kHalfBytes, &tm_k, bar(kBarKVFull + slot), 64, c1(hm, row), c2(hm, row), img);
           }
         }
         if (!ok) {
@@ -296,39 +307,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
         bool ok = wait_bar(bar(kBarQFull + 0), 0, abort_flag, a.status, kStMma) &&
                   wait_bar(bar(kBarQFull + 1), 0, abort_flag, a.status, kStMma);
-        uint32_t it = 0;
         if (ok) ok = wait_bar(bar(kBarKVFull + 0), 0, abort_flag, a.status, kStMma);
         if (ok) {
           tc_fence_after();
-          const uint32_t k_addr = base + kOffKV;
+          const uint32_t k_addr = base + kOffKV + kTileBytes;  // pair 0: K_0 in the second half of slot 0
           issue_qk(0, k_addr);
           umma_commit(bar(kBarSFull + 0));
           issue_qk(1, k_addr);
           umma_commit(bar(kBarSFull + 1));
           umma_commit(bar(kBarKVEmpty + 0));
-          it = 1;
         }
         for (int jj = 0; jj < n_act && ok; ++jj) {
-          const uint32_t sv = it % kStages;
-          const uint32_t phv = (it / kStages) & 1u;
-          ++it;
+          // Pair jj + 1: V of this step's tile and K of the next step's.
+          const uint32_t pair = static_cast<uint32_t>(jj) + 1u;
+          const uint32_t slot = pair % kPairStages;
           stamp(4, jj, 0);
-          ok = wait_bar(bar(kBarKVFull + sv), phv, abort_flag, a.status, kStMma);
+          ok = wait_bar(bar(kBarKVFull + slot), (pair / kPairStages) & 1u, abort_flag, a.status, kStMma);
           if (!ok) break;
           stamp(4, jj, 1);
           const bool has_next = (jj + 1 < n_act);
-          uint32_t sk = 0;
-          if (has_next) {
-            sk = it % kStages;
-            const uint32_t phk = (it / kStages) & 1u;
-            ++it;
-            ok = wait_bar(bar(kBarKVFull + sk), phk, abort_flag, a.status, kStMma);
-            if (!ok) break;
-          }
           stamp(4, jj, 2);
           tc_fence_after();
-          const uint32_t v_addr = base + kOffKV + sv * kTileBytes;
-          const uint32_t k_addr = base + kOffKV + sk * kTileBytes;
+          const uint32_t v_addr = base + kOffKV + slot * 2 * kTileBytes;
+          const uint32_t k_addr = v_addr + kTileBytes;
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             stamp(0, jj, 4 * t + 0);
@@ -351,8 +352,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             stamp(0, jj, 4 * t + 3);
           }
           if (!ok) break;
-          umma_commit(bar(kBarKVEmpty + sv));
-          if (has_next) umma_commit(bar(kBarKVEmpty + sk));
+          umma_commit(bar(kBarKVEmpty + slot));
         }
         if (!ok) {
           // Wait (bounded) for MMAs already issued before TMEM is released.
