@@ -89,6 +89,7 @@ constexpr int kTileIndexMask = 0x3FFFFFFF;
 
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                          uint32_t* status, uint32_t code) {
+  if (mbar_test_wait(bar, parity)) return true;  // the common case for the MMA-issuing thread
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
