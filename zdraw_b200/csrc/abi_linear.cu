@@ -22,6 +22,7 @@ struct PartSpec {
   unsigned int* row_key = nullptr;   // row max / exp: ordered keys of the row maxima
   float* row_sum = nullptr;          // exp: partial row sums
   float exp_scale = 0.0f;
+  uint32_t n_valid = 0;              // row max / exp: real columns (0 = all n); W then has n_valid rows
 };
 
 // Shared body of zdraw_cuda_linear and zdraw_cuda_qkv_projection: validates, builds the tensor
@@ -29,7 +30,8 @@ struct PartSpec {
 // operands_e4m3 (internal, the row-max pass of the wide attention): A and W hold e4m3 bytes instead
 // of halves; p->a_dtype / w_dtype still say f16 and strides count elements.
 int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec* parts, const float* rope_cos,
-               const float* rope_sin, const zdraw_cuda_linear_params* p, bool operands_e4m3 = false) {
+               const float* rope_sin, const zdraw_cuda_linear_params* p, bool operands_e4m3 = false,
+               uint32_t w_k_valid = 0) {  // columns of W that exist when fewer than k (A has all k)
   if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
   if (p->reserved != 0 || p->m == 0 || p->n == 0 || p->k == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero size or reserved != 0");
   if (p->c_dtype != ZDRAW_DTYPE_F16 && p->c_dtype != ZDRAW_DTYPE_F32) return fail(cx, ZDRAW_CUDA_E_ARG, "bad c_dtype");
@@ -48,9 +50,10 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
   if (operands_e4m3 && p->k % 128 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "k must be a multiple of 128 for 8-bit operands");
   if (p->m > (1u << 30) || p->n > (1u << 30) || p->k > (1u << 30)) return fail(cx, ZDRAW_CUDA_DECLINED, "shape too large");
   const long long ld_a = p->ld_a ? static_cast<long long>(p->ld_a) : p->k;
-  const long long ld_w = p->ld_w ? static_cast<long long>(p->ld_w) : p->k;
+  const long long ld_w = p->ld_w ? static_cast<long long>(p->ld_w) : (w_k_valid ? w_k_valid : p->k);
   const long long ld_c = p->ld_c ? static_cast<long long>(p->ld_c) : p->n;
-  if (ld_a < p->k || ld_w < p->k || ld_c < p->n) return fail(cx, ZDRAW_CUDA_E_ARG, "row stride smaller than the row");
+  if (ld_a < p->k || ld_w < static_cast<long long>(w_k_valid ? w_k_valid : p->k) || ld_c < p->n)
+    return fail(cx, ZDRAW_CUDA_E_ARG, "row stride smaller than the row");
   const long long ld_align = operands_e4m3 ? 16 : 8;  // TMA strides are multiples of 16 bytes
   if (ld_a % ld_align != 0 || ld_w % ld_align != 0 || ld_c % 8 != 0)
     return fail(cx, ZDRAW_CUDA_DECLINED, "row strides must be multiples of 8 elements (16 for 8-bit operands)");
@@ -91,6 +94,7 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
       lp.row_key = parts[i].row_key;
       lp.row_sum = parts[i].row_sum;
       lp.exp_scale = parts[i].exp_scale;
+      lp.n_valid = static_cast<int>(parts[i].n_valid ? parts[i].n_valid : p->n);
     }
   }
   ZD_CUDA(cx, cudaSetDevice(cx->device));
@@ -98,8 +102,9 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
   zdraw::LinearMaps maps;
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const cuuint64_t esz = operands_e4m3 ? 1u : 2u;
-  auto encode = [&](CUtensorMap* tm, const void* base_ptr, uint64_t rows, long long ld) {
-    const cuuint64_t dims[4] = {p->k, rows, 1, 1};
+  // Rows and columns beyond what a matrix has are filled with zeros by the copy engine.
+  auto encode = [&](CUtensorMap* tm, const void* base_ptr, uint64_t rows, long long ld, uint64_t cols) {
+    const cuuint64_t dims[4] = {cols, rows, 1, 1};
     const cuuint64_t strides[3] = {esz * static_cast<cuuint64_t>(ld), esz * static_cast<cuuint64_t>(ld) * rows,
                                    esz * static_cast<cuuint64_t>(ld) * rows};
     const cuuint32_t box[4] = {operands_e4m3 ? 128u : 64u, 128, 1, 1};  // 128-byte rows either way
@@ -108,10 +113,12 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   };
-  if (encode(&maps.a, a, p->m, ld_a) != CUDA_SUCCESS) return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
-  for (int i = 0; i < zdraw::kMaxLinearParts; ++i)
-    if (encode(&maps.w[i], parts[i < n_parts ? i : 0].w, p->n, ld_w) != CUDA_SUCCESS)
+  if (encode(&maps.a, a, p->m, ld_a, p->k) != CUDA_SUCCESS) return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
+  for (int i = 0; i < zdraw::kMaxLinearParts; ++i) {
+    const PartSpec& ps = parts[i < n_parts ? i : 0];
+    if (encode(&maps.w[i], ps.w, ps.n_valid ? ps.n_valid : p->n, ld_w, w_k_valid ? w_k_valid : p->k) != CUDA_SUCCESS)
       return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed");
+  }
   // Plain parts: C for the epilogue's tile stores (32 columns x 32 rows, swizzle of the row size).
   for (int i = 0; i < zdraw::kMaxLinearParts; ++i) {
     maps.c[i] = maps.a;  // any valid map where none is used
@@ -156,15 +163,18 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   // Shapes outside the kernels are declined (the reference's own admission is tokens % 32 and
   // head_dim % 32, src/metal/mvattn_owned.zig:271-272): both products run on the 256-column tiles
   // of the projection kernel; the token bound keeps the tokens^2 half scratch below 9 GB.
-  if (tokens % 256 != 0 || head_dim % 256 != 0 || tokens > 65536 || head_dim > 4096)
-    return fail(cx, ZDRAW_CUDA_DECLINED, "tokens and head_dim must be multiples of 256, tokens <= 65536");
+  if (tokens % 64 != 0 || head_dim % 256 != 0 || tokens > 65536 || head_dim > 4096)
+    return fail(cx, ZDRAW_CUDA_DECLINED, "tokens must be a multiple of 64 (<= 65536) and head_dim of 256");
   ZD_CUDA(cx, cudaSetDevice(cx->device));
   const size_t n = tokens * head_dim;
-  const size_t n_partial = 2 * (tokens / 256);  // partial row sums: one per 128-column half tile
+  // The score matrix is tiled in blocks of 256 keys: its columns are padded to that (the padding
+  // is stored as zeros and skipped by the row maximum).
+  const size_t n_pad = (tokens + 255) / 256 * 256;
+  const size_t n_partial = 2 * (n_pad / 256);  // partial row sums: one per 128-column half tile
   const size_t aux_bytes = tokens * 4 * (2 + n_partial);  // row keys, 1/row sum, partial sums
   int rc;
   if ((rc = ensure(cx, cx->wa_q16, n * 2)) || (rc = ensure(cx, cx->wa_k16, n * 2)) || (rc = ensure(cx, cx->wa_vt16, n * 2)) ||
-      (rc = ensure(cx, cx->wa_aux, aux_bytes)) || (rc = ensure(cx, cx->wa_p, tokens * tokens * 2)) ||
+      (rc = ensure(cx, cx->wa_aux, aux_bytes)) || (rc = ensure(cx, cx->wa_p, tokens * n_pad * 2)) ||
       (rc = ensure(cx, cx->wa_q8, n)) || (rc = ensure(cx, cx->wa_k8, n)))
     return rc;
   unsigned int* row_key = static_cast<unsigned int*>(cx->wa_aux.p);
@@ -185,11 +195,12 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   // to the half range.
   zdraw_cuda_linear_params ps = {};
   ps.m = static_cast<uint32_t>(tokens);
-  ps.n = static_cast<uint32_t>(tokens);
+  ps.n = static_cast<uint32_t>(n_pad);
   ps.k = static_cast<uint32_t>(head_dim);
   ps.a_dtype = ps.w_dtype = ps.c_dtype = ZDRAW_DTYPE_F16;
   PartSpec part_s = {cx->wa_k16.p, cx->wa_p.p, static_cast<uint32_t>(zdraw::kEpilogueRowMax), nullptr, nullptr};
   part_s.row_key = row_key;
+  part_s.n_valid = static_cast<uint32_t>(tokens);
   part_s.w = cx->wa_k8.p;
   if ((rc = run_linear(cx, stream, cx->wa_q8.p, 1, &part_s, nullptr, nullptr, &ps, true)) != 0) return rc;
   part_s.w = cx->wa_k16.p;
@@ -202,12 +213,13 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   zdraw_cuda_linear_params po = {};
   po.m = static_cast<uint32_t>(tokens);
   po.n = static_cast<uint32_t>(head_dim);
-  po.k = static_cast<uint32_t>(tokens);
+  po.k = static_cast<uint32_t>(n_pad);   // P with its zero padding; V^T has `tokens` columns, the rest reads as zeros
+  po.ld_w = tokens;
   po.a_dtype = po.w_dtype = ZDRAW_DTYPE_F16;
   po.c_dtype = ZDRAW_DTYPE_F32;
   PartSpec part_o = {cx->wa_vt16.p, o, 0, nullptr, nullptr};
   part_o.row_scale = row_inv;
-  return run_linear(cx, stream, cx->wa_p.p, 1, &part_o, nullptr, nullptr, &po);
+  return run_linear(cx, stream, cx->wa_p.p, 1, &part_o, nullptr, nullptr, &po, false, static_cast<uint32_t>(tokens));
 }
 
 int zdraw_cuda_qkv_projection(void* ctx, void* stream, const void* x, const void* wq, const void* wk, const void* wv,

@@ -273,8 +273,15 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
           uint32_t x[32];
           tmem_ld_x32(t_acc + 128u * hh + 32u * pc, x);
           tmem_wait_ld();
+          const int col0 = tile_n * kTN + 128 * hh + 32 * pc;
+          if (col0 + 32 <= part.n_valid) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+            for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+          } else {  // the ragged end of the row (at most once per row)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < part.n_valid) mx = fmaxf(mx, __uint_as_float(x[i]));
+          }
         }
         if (live) atomicMax(part.row_key + m, float_key(mx));
       } else if (part.epilogue == kEpiloguePlain || part.epilogue == kEpilogueExp) {
@@ -325,11 +332,14 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
             const int sw = (lane >> 1) & 3;
             uint32_t h[16];
             if (exp_mode) {
+              const int n_live = part.n_valid - (col_base + 32 * pc);  // columns of this piece that exist
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
                 // (the subtracted maximum may be an estimate: keep the result in the half range)
-                const float e0 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias)), kHalfMax);
-                const float e1 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias)), kHalfMax);
+                float e0 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias)), kHalfMax);
+                float e1 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias)), kHalfMax);
+                if (2 * i >= n_live) e0 = 0.0f;
+                if (2 * i + 1 >= n_live) e1 = 0.0f;
                 psum += e0 + e1;  // f32 sum of the unrounded values, as the reference's softmax takes it
                 const __half2 v = __floats2half2_rn(e0, e1);
                 h[i] = *reinterpret_cast<const uint32_t*>(&v);

@@ -28,6 +28,9 @@ struct LinearPart {
   unsigned int* row_key;
   float* row_sum;
   float exp_scale;
+  // row max / exp: columns at and beyond n_valid are padding of the last column block (W has no
+  // such rows): they do not count for the maximum and are stored as zeros.
+  int n_valid;
 };
 
 // Up to three products that share A (the Q, K and V projections of one activation) run as one
