@@ -265,7 +265,8 @@ ZDRAW_CUDA_API int zdraw_cuda_last_status(void *ctx, void *stream, uint32_t *dev
  *               is the head-major [image][head][token][128] buffer zdraw_cuda_attention takes
  *               with qk_layout = ZDRAW_LAYOUT_HEAD_MAJOR: the q/k projection and krms_rope_hm in
  *               one pass, without the reference's f32 q/k round trip through memory.
- * n must be a multiple of 256 and k of 64, else the call is declined.
+ * n and k must be multiples of 32 (the reference's own admission for its fast GEMMs,
+ * src/metal/mres_util.zig:30-38), else the call is declined; any m.
  */
 typedef struct zdraw_cuda_linear_params {
   uint32_t m, n, k;

@@ -28,7 +28,8 @@ def make(m, n, k, seed):
     return a, w
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 256, 512), (1, 512, 128), (257, 768, 320)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 256, 512), (1, 512, 128), (257, 768, 320),
+                                   (300, 96, 160), (257, 352, 96), (64, 32, 32), (513, 288, 3104)])
 @pytest.mark.parametrize("c_dtype", [3, 1])
 def test_plain_epilogue_matches_cpu(ctx, oracle, m, n, k, c_dtype):
     a, w = make(m, n, k, m + n + k)
@@ -52,10 +53,10 @@ def test_plain_epilogue_matches_cpu(ctx, oracle, m, n, k, c_dtype):
 def test_declines_and_rejects(ctx):
     x = torch.zeros((256, 256), dtype=torch.float16, device="cuda")
     out = torch.zeros((256, 256), dtype=torch.float32, device="cuda")
+    with pytest.raises(mattn.UnsupportedShape):  # n and k must be multiples of 32, as in the reference
+        ctx.linear(x, x, out, _lib.LinearParams(m=256, n=200, k=256, a_dtype=1, w_dtype=1, c_dtype=3))
     with pytest.raises(mattn.UnsupportedShape):
-        ctx.linear(x, x, out, _lib.LinearParams(m=256, n=128, k=256, a_dtype=1, w_dtype=1, c_dtype=3))
-    with pytest.raises(mattn.UnsupportedShape):
-        ctx.linear(x, x, out, _lib.LinearParams(m=256, n=256, k=96, a_dtype=1, w_dtype=1, c_dtype=3))
+        ctx.linear(x, x, out, _lib.LinearParams(m=256, n=256, k=104, a_dtype=1, w_dtype=1, c_dtype=3))
     with pytest.raises(mattn.UnsupportedShape):
         ctx.linear(x, x, out, _lib.LinearParams(m=256, n=256, k=256, a_dtype=3, w_dtype=1, c_dtype=3))
     with pytest.raises(mattn.InvalidShape):
@@ -65,7 +66,7 @@ def test_declines_and_rejects(ctx):
                                                 tokens=256, heads=2))
 
 
-@pytest.mark.parametrize("batch,tokens,heads,txt,k", [(1, 80, 2, 16, 256), (2, 300, 4, 100, 128)])
+@pytest.mark.parametrize("batch,tokens,heads,txt,k", [(1, 80, 2, 16, 256), (2, 300, 4, 100, 128), (1, 130, 3, 30, 96)])
 def test_qk_epilogue_matches_projection_then_prologue(ctx, oracle, batch, tokens, heads, txt, k):
     n, m = heads * 128, batch * tokens
     a, w = make(m, n, k, tokens)

@@ -46,8 +46,9 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
   // Shapes and types outside the kernel: declined, nothing enqueued (the reference's fast GEMMs
   // admit 32-aligned dims only, src/metal/mres_util.zig:30-38).
   if (p->a_dtype != ZDRAW_DTYPE_F16 || p->w_dtype != ZDRAW_DTYPE_F16) return fail(cx, ZDRAW_CUDA_DECLINED, "A and W must be f16");
-  if (p->n % 256 != 0 || p->k % 64 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "n must be a multiple of 256 and k of 64");
-  if (operands_e4m3 && p->k % 128 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "k must be a multiple of 128 for 8-bit operands");
+  // (Tiles are 256 columns x 64 of K; what lies beyond n or k is zero-filled on the way in and
+  // clipped on the way out, so only the 16-byte granularity of the copy engine remains.)
+  if (p->n % 32 != 0 || p->k % 32 != 0) return fail(cx, ZDRAW_CUDA_DECLINED, "n and k must be multiples of 32");
   if (p->m > (1u << 30) || p->n > (1u << 30) || p->k > (1u << 30)) return fail(cx, ZDRAW_CUDA_DECLINED, "shape too large");
   const long long ld_a = p->ld_a ? static_cast<long long>(p->ld_a) : p->k;
   const long long ld_w = p->ld_w ? static_cast<long long>(p->ld_w) : (w_k_valid ? w_k_valid : p->k);

@@ -119,10 +119,11 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_cta_rank();  // 0: issues the pair's MMAs
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int tiles_n = a.n / kTN;                        // column blocks of one part
+  const int tiles_n = (a.n + kTN - 1) / kTN;            // column blocks of one part (the last may be partial)
   const int tiles_m = (a.m + 2 * kTM - 1) / (2 * kTM);  // pair tiles: 256 rows
   const int n_tiles = tiles_m * tiles_n * a.n_parts;
-  const int k_steps = a.fp8 ? a.k / (2 * kTK) : a.k / kTK;  // a stage is a 128-byte slice of K per row
+  // A stage is a 128-byte slice of K per row; rows, columns and K beyond the matrices read as zeros.
+  const int k_steps = a.fp8 ? (a.k + 2 * kTK - 1) / (2 * kTK) : (a.k + kTK - 1) / kTK;
   const int k_per_stage = a.fp8 ? 2 * kTK : kTK;
 
   if (threadIdx.x == 0) {
@@ -373,7 +374,7 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
 #pragma unroll
         for (int it = 0; it < 4; ++it) roff[it] = __shfl_sync(0xffffffffu, my_off, it * 8 + (lane >> 2)) + 4 * (lane & 3);
         float4* tab = reinterpret_cast<float4*>(smem_raw + kOffTab + (warp - 4) * kTabBytesPerWarp);
-        {
+        if (tile_n * 2 + hh < a.heads) {  // an odd head count leaves the last tile's second half empty
           const int head = tile_n * 2 + hh;
           const uint32_t t_head = t_acc + 128u * hh;
           // pass 1: sum of squares over the head's 128 columns (f32, as the reference's GPU kernels)
@@ -473,7 +474,7 @@ cudaError_t linear_configure() {
 }
 
 cudaError_t launch_linear(cudaStream_t stream, const LinearMaps& maps, const LinearArgs& args, int sm_count) {
-  const int n_tiles = ((args.m + 2 * kTM - 1) / (2 * kTM)) * (args.n / kTN) * args.n_parts;
+  const int n_tiles = ((args.m + 2 * kTM - 1) / (2 * kTM)) * ((args.n + kTN - 1) / kTN) * args.n_parts;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;

@@ -35,8 +35,8 @@ struct LinearPart {
 
 // Up to three products that share A (the Q, K and V projections of one activation) run as one
 // launch over n_parts * (n / 256) column blocks. A and every W are reached through tensor maps
-// (f16, 128-byte swizzle, boxes of 64 columns x 128 rows; e4m3: boxes of 128 columns). n % 256 == 0,
-// k % 64 == 0 (f16) or k % 128 == 0 (e4m3).
+// (f16, 128-byte swizzle, boxes of 64 columns x 128 rows; e4m3: boxes of 128 columns). Tiles are
+// 256 columns x 64 (e4m3: 128) of K; partial tiles read zeros beyond the matrices.
 struct LinearArgs {
   int m, n, k;
   int fp8;  // 1: A and W are e4m3 bytes (k % 128 == 0), a 128-byte swizzled row holds 128 elements
