@@ -312,8 +312,8 @@ ZDRAW_CUDA_API int zdraw_cuda_qkv_projection(void *ctx, void *stream, const void
  * 1024 px). Replaces mvattn_owned.run in its product tier (src/metal/mvattn_owned.zig:259-330:
  * half Q, K, V^T; S = Q K^T with f32 accumulation; f32 row softmax with scale 1/sqrt(head_dim)
  * giving half P; O = P V with f32 output), full, non-causal, no mask. q, k, v, o are DEVICE
- * pointers to [tokens][head_dim] f32. tokens must be a multiple of 64 (<= 65536) and head_dim of
- * 256, else the call is declined. Scratch (half operands, tokens^2 half exp(scores),
+ * pointers to [tokens][head_dim] f32. tokens (<= 65536) and head_dim (<= 4096) must be multiples
+ * of 32, as the reference requires; else the call is declined. Scratch (half operands, tokens^2 half exp(scores),
  * e4m3 copies of Q and K for a first estimate of the row maxima, row statistics: 0.6 GB at 16384
  * tokens) is grow-only context memory; the f32 scores are never stored.
  */

@@ -25,7 +25,7 @@ def make(tokens, dim, seed, scale=1.0):
     return tuple(torch.randn((tokens, dim), generator=g, device="cuda") * scale for _ in range(3))
 
 
-@pytest.mark.parametrize("tokens,dim", [(256, 256), (768, 512), (1024, 512), (64, 256), (320, 512), (1600, 512)])
+@pytest.mark.parametrize("tokens,dim", [(256, 256), (768, 512), (1024, 512), (64, 256), (320, 512), (1600, 512), (96, 64), (160, 320), (32, 32)])
 def test_small_shapes_match_cpu_attention(ctx, oracle, tokens, dim):
     q, k, v = make(tokens, dim, tokens + dim)
     out = torch.full((tokens, dim), float("nan"), device="cuda")
@@ -101,13 +101,15 @@ def test_constant_values_and_peaked_scores(ctx):
 
 
 def test_shapes_outside_the_kernels_are_declined(ctx):
-    x = torch.zeros((288, 512), device="cuda")
+    x = torch.zeros((280, 512), device="cuda")
     o = torch.empty_like(x)
     with pytest.raises(mattn.UnsupportedShape):
-        ctx.wide_attention(x, x, x, o, mattn.Config(288, 1, 1, 512))  # tokens % 64 != 0
-    y = torch.zeros((256, 128), device="cuda")
+        ctx.wide_attention(x, x, x, o, mattn.Config(280, 1, 1, 512))  # tokens % 32 != 0
+    y = torch.zeros((256, 120), device="cuda")
     with pytest.raises(mattn.UnsupportedShape):
-        ctx.wide_attention(y, y, y, torch.empty_like(y), mattn.Config(256, 1, 1, 128))  # head_dim % 256 != 0
+        ctx.wide_attention(y, y, y, torch.empty_like(y), mattn.Config(256, 1, 1, 120))  # head_dim % 32 != 0
+    x = torch.zeros((256, 512), device="cuda")
+    o = torch.empty_like(x)
     with pytest.raises(mattn.UnsupportedShape):
         ctx.wide_attention(x, x, x, o, mattn.Config(256, 2, 2, 512))  # more than one head
     with pytest.raises(mattn.UnsupportedShape):

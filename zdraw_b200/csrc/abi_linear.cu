@@ -161,11 +161,11 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   if (!q || !k || !v || !o || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o))
     return fail(cx, ZDRAW_CUDA_E_ARG, "null or misaligned tensor");
   if (tokens == 0 || head_dim == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero tokens or head_dim");
-  // Shapes outside the kernels are declined (the reference's own admission is tokens % 32 and
-  // head_dim % 32, src/metal/mvattn_owned.zig:271-272): both products run on the 256-column tiles
-  // of the projection kernel; the token bound keeps the tokens^2 half scratch below 9 GB.
-  if (tokens % 64 != 0 || head_dim % 256 != 0 || tokens > 65536 || head_dim > 4096)
-    return fail(cx, ZDRAW_CUDA_DECLINED, "tokens must be a multiple of 64 (<= 65536) and head_dim of 256");
+  // Shapes outside the kernels are declined: the reference's own admission, tokens % 32 and
+  // head_dim % 32 (src/metal/mvattn_owned.zig:271-272); the token bound keeps the tokens^2 half
+  // scratch below 9 GB.
+  if (tokens % 32 != 0 || head_dim % 32 != 0 || tokens > 65536 || head_dim > 4096)
+    return fail(cx, ZDRAW_CUDA_DECLINED, "tokens (<= 65536) and head_dim (<= 4096) must be multiples of 32");
   ZD_CUDA(cx, cudaSetDevice(cx->device));
   const size_t n = tokens * head_dim;
   // The score matrix is tiled in blocks of 256 keys: its columns are padded to that (the padding
