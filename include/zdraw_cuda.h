@@ -186,7 +186,10 @@ ZDRAW_CUDA_API int zdraw_cuda_joint_attention_host(void *ctx, const void *q, con
  *     library holds the 64 MiB until the process exits.
  *   - The CUDA device of `stream` must be current. The first call on a device looks up the
  *     array's device address (cudaGetSymbolAddress) and configures the kernel; make that first
- *     call before starting any stream capture.
+ *     call before starting any stream capture. That first use also makes the CUDA runtime load
+ *     the part of the library's device image that holds the array: the device's free memory
+ *     drops by the 64 MiB then, once, and by nothing on later calls. A caller with a fixed
+ *     budget makes the first call (or a zdraw_cuda_static_last_status call) during start-up.
  *   - All calls share the one array and one status word (cleared on the stream at the start of
  *     each call): calls that overlap on the GPU race. Keep them on one stream or order them.
  *   - `error_text`, if not NULL, receives a static string describing a refusal or failure.
@@ -198,6 +201,16 @@ ZDRAW_CUDA_API int zdraw_cuda_joint_attention_static(void *stream, const void *q
                                                      const float *rope_sin, void *o,
                                                      const zdraw_cuda_attn_params *p,
                                                      const char **error_text);
+
+/*
+ * The status word of zdraw_cuda_joint_attention_static on the current device, the counterpart
+ * of zdraw_cuda_last_status for the call that has no context (like it, no counterpart in the
+ * reference). Synchronises `stream`, copies the word (4 bytes; nothing is allocated) and clears
+ * it when it is non-zero. 0 = the kernels of the last static call ran to the end; non-zero = a
+ * kernel gave up a bounded wait and that call's output is invalid. Every static call clears the
+ * word when it starts, so read it before the next static call on that device.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_static_last_status(void *stream, uint32_t *device_status);
 
 /*
  * Attention alone with HOST buffers (no prologue): q, k, v in in_dtype, token-major;
@@ -220,15 +233,18 @@ ZDRAW_CUDA_API int zdraw_cuda_klein_rope_table(float *cos_out, float *sin_out, s
 
 /*
  * Z-Image: zrope.Cache.init + per-token gather (src/zimage/zrope.zig:32-38,
- * 88-116) for the unified sequence [image | caption] with positions image
- * (cap_total+1, r, c) and caption (1+i, 0, 0) (src/zimage/zunify.zig:16-37,
- * zstep_shape.zig:58-66). dims/lens are the three axis sizes (sum(dims) == 128).
- * Returns -1 for a configuration or position the reference rejects
+ * 88-116) for the unified sequence [image | image pad | caption] with positions image
+ * (cap_total+1, r, c), image pad slots (0, 0, 0) and caption (1+i, 0, 0) over the padded
+ * caption length (src/zimage/zunify.zig:16-37, zstep_shape.zig:33-46, 58-66; zseq.zig:36-61:
+ * the image stream is padded to a multiple of 32 tokens and its pad slots sit at the origin).
+ * img_pad is the number of those slots, (32 - img_h*img_w % 32) % 32 in the reference; the
+ * tables have img_h*img_w + img_pad + cap_total rows. dims/lens are the three axis sizes
+ * (sum(dims) == 128). Returns -1 for a configuration or position the reference rejects
  * (InvalidConfig / BadPosition).
  */
 ZDRAW_CUDA_API int zdraw_cuda_zimage_rope_table(float *cos_out, float *sin_out, size_t img_h, size_t img_w,
-                                 size_t cap_total, const size_t dims[3], const size_t lens[3],
-                                 float theta);
+                                 size_t img_pad, size_t cap_total, const size_t dims[3],
+                                 const size_t lens[3], float theta);
 
 /*
  * The same two tables built on the GPU, written to DEVICE memory on the caller's stream, so a
@@ -243,8 +259,9 @@ ZDRAW_CUDA_API int zdraw_cuda_klein_rope_table_device(void *ctx, void *stream, f
                                                       size_t txt_len, size_t grid_h, size_t grid_w, size_t ref_h,
                                                       size_t ref_w, double theta);
 ZDRAW_CUDA_API int zdraw_cuda_zimage_rope_table_device(void *ctx, void *stream, float *cos_dev, float *sin_dev,
-                                                       size_t img_h, size_t img_w, size_t cap_total,
-                                                       const size_t dims[3], const size_t lens[3], float theta);
+                                                       size_t img_h, size_t img_w, size_t img_pad,
+                                                       size_t cap_total, const size_t dims[3],
+                                                       const size_t lens[3], float theta);
 
 /*
  * Reads (and clears) the device status word. 0 = every kernel ran to the end.

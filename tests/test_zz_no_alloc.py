@@ -59,7 +59,11 @@ def test_static_scratch_entry_point_matches_regular_call_twice():
             torch.cuda.synchronize()
             if i == 1:
                 assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the free device memory"
-            assert ctx.last_status() == 0
+            # The static path has its own status word (the context's is never touched by it).
+            word = C.c_uint32(0xFFFFFFFF)
+            stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            assert lib.zdraw_cuda_static_last_status(stream, C.byref(word)) == 0
+            assert word.value == 0, f"a kernel of the static call gave up a wait (status {word.value:#x})"
             # Same kernels, same inputs, same reduction order: the bytes must agree (the tolerance the
             # other tests use against the oracle, 1e-2 max-abs, is implied by equality).
             assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"call {i} differs"

@@ -75,10 +75,11 @@ SYMBOLS = {
     "zdraw_cuda_joint_attention_host": (C.c_int, [_VP] * 12 + [_PP]),
     "zdraw_cuda_attention_host": (C.c_int, [_VP] * 6 + [_PP]),
     "zdraw_cuda_joint_attention_static": (C.c_int, [_VP] * 11 + [_PP, C.POINTER(C.c_char_p)]),
+    "zdraw_cuda_static_last_status": (C.c_int, [_VP, C.POINTER(C.c_uint32)]),
     "zdraw_cuda_klein_rope_table": (C.c_int, [_VP, _VP] + [C.c_size_t] * 5 + [C.c_double]),
-    "zdraw_cuda_zimage_rope_table": (C.c_int, [_VP, _VP] + [C.c_size_t] * 3 + [_VP, _VP, C.c_float]),
+    "zdraw_cuda_zimage_rope_table": (C.c_int, [_VP, _VP] + [C.c_size_t] * 4 + [_VP, _VP, C.c_float]),
     "zdraw_cuda_klein_rope_table_device": (C.c_int, [_VP] * 4 + [C.c_size_t] * 5 + [C.c_double]),
-    "zdraw_cuda_zimage_rope_table_device": (C.c_int, [_VP] * 4 + [C.c_size_t] * 3 + [_VP, _VP, C.c_float]),
+    "zdraw_cuda_zimage_rope_table_device": (C.c_int, [_VP] * 4 + [C.c_size_t] * 4 + [_VP, _VP, C.c_float]),
     "zdraw_cuda_last_status": (C.c_int, [_VP, _VP, C.POINTER(C.c_uint32)]),
     "zdraw_cuda_linear": (C.c_int, [_VP] * 9 + [C.POINTER(LinearParams)]),
     "zdraw_cuda_qkv_projection": (C.c_int, [_VP] * 15 + [C.POINTER(LinearParams)]),

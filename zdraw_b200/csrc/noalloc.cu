@@ -16,9 +16,14 @@
 //     with ZDRAW_CUDA_DECLINED and a message, nothing is enqueued;
 //   - every call uses the same array. It still holds the previous call's q/k when a call starts
 //     (each call overwrites the part it reads, so nothing needs clearing there; the status word
-//     is cleared on the stream at the start of every call). Two calls that overlap on the GPU
-//     (different streams, no dependency between them) race on the array and on the status word:
-//     give them one stream or order them with events.
+//     is cleared on the stream at the start of every call, so a caller that wants to know
+//     whether a call ran to the end reads it with zdraw_cuda_static_last_status BEFORE making
+//     the next call). Two calls that overlap on the GPU (different streams, no dependency
+//     between them) race on the array and on the status word: give them one stream or order
+//     them with events;
+//   - the array is part of the library's device image: the first use of this file on a device
+//     (the first call, or the first status read) makes the CUDA runtime load that image, which
+//     takes the 64 MiB from the device's free memory. Make it during start-up.
 #include <cuda.h>
 #include <cuda_runtime.h>
 
@@ -233,6 +238,24 @@ int zdraw_cuda_joint_attention_static(void* stream, const void* q, const void* k
   a.status = st->status;
   a.trace = nullptr;
   if (zdraw::launch_attn_fwd(s, tm_q, tm_k, tm_v, tm_q, a) != cudaSuccess) return fail(ZDRAW_CUDA_E_CUDA, "attention launch failed");
+  return ZDRAW_CUDA_OK;
+}
+
+// The status word of the static path on the current device: waits for `stream`, copies the word
+// to the host (4 bytes, no allocation) and clears it when it is non-zero.
+int zdraw_cuda_static_last_status(void* stream, uint32_t* device_status) {
+  g_last_error = "";
+  if (!device_status) return fail(ZDRAW_CUDA_E_ARG, "device_status is null");
+  *device_status = 0;
+  DeviceState* st = nullptr;
+  int rc = setup_current_device(&st);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaStreamSynchronize(s) != cudaSuccess) return fail(ZDRAW_CUDA_E_CUDA, "cudaStreamSynchronize failed");
+  if (cudaMemcpy(device_status, st->status, sizeof(uint32_t), cudaMemcpyDeviceToHost) != cudaSuccess)
+    return fail(ZDRAW_CUDA_E_CUDA, "reading the status word failed");
+  if (*device_status != 0 && cudaMemset(st->status, 0, sizeof(uint32_t)) != cudaSuccess)
+    return fail(ZDRAW_CUDA_E_CUDA, "clearing the status word failed");
   return ZDRAW_CUDA_OK;
 }
 

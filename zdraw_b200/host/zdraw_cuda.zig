@@ -189,6 +189,9 @@ pub extern fn zdraw_cuda_joint_attention_static(
     params: *const AttnParams,
     error_text: ?*[*:0]const u8,
 ) c_int;
+// Status word of the static call on the current device (read and cleared; read it before the
+// next static call, which clears it when it starts). Allocates nothing.
+pub extern fn zdraw_cuda_static_last_status(stream: ?*anyopaque, status: *u32) c_int;
 // Debugging: pipeline clock stamps of one CTA into a device buffer of >= 1600 u64 words (null = off).
 pub extern fn zdraw_cuda_attn_set_trace(ctx: *anyopaque, device_words: ?*anyopaque, n_words: usize) c_int;
 pub extern fn zdraw_cuda_last_status(ctx: *anyopaque, stream: ?*anyopaque, status: *u32) c_int;
@@ -209,6 +212,7 @@ pub extern fn zdraw_cuda_zimage_rope_table(
     sin_out: [*]f32,
     img_h: usize,
     img_w: usize,
+    img_pad: usize,
     cap_total: usize,
     dims: *const [3]usize,
     lens: *const [3]usize,
@@ -234,6 +238,7 @@ pub extern fn zdraw_cuda_zimage_rope_table_device(
     sin_dev: [*]f32,
     img_h: usize,
     img_w: usize,
+    img_pad: usize,
     cap_total: usize,
     dims: *const [3]usize,
     lens: *const [3]usize,
