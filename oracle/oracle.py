@@ -60,7 +60,7 @@ def lib() -> C.CDLL:
         _lib.orc_zrope_fill.restype = C.c_int
         _lib.orc_zrope_apply.argtypes = [fp, fp, fp, fp, fp]
         _lib.orc_zrope_apply.restype = C.c_int
-        _lib.orc_zimage_positions.argtypes = [fp, sz, sz, sz]
+        _lib.orc_zimage_positions.argtypes = [fp, sz, sz, sz, sz]
         _lib.orc_zimage_positions.restype = None
         _lib.orc_zrope_expand.argtypes = [fp, fp, fp, fp, fp, fp, sz]
         _lib.orc_zrope_expand.restype = C.c_int
@@ -213,10 +213,17 @@ def zrope_apply(vec, values, dims, lens, pos) -> np.ndarray:
     return vec
 
 
-def zimage_positions(img_h: int, img_w: int, cap_total: int) -> np.ndarray:
-    """Unified Z-Image positions, image first (src/zimage/zunify.zig:16-37)."""
-    pos = np.zeros((img_h * img_w + cap_total, 3), dtype=np.uintp)
-    lib().orc_zimage_positions(_p(pos), img_h, img_w, cap_total)
+def zimage_pad_len(tokens: int) -> int:
+    """``zseq.padLen`` (src/zimage/zseq.zig:15-17)."""
+    return (32 - tokens % 32) % 32
+
+
+def zimage_positions(img_h: int, img_w: int, cap_total: int, img_pad=None) -> np.ndarray:
+    """Unified Z-Image positions [image | image pad | caption] (src/zimage/zunify.zig:16-37,
+    zseq.zig:36-61); ``img_pad`` defaults to the reference's padding to a multiple of 32."""
+    img_pad = zimage_pad_len(img_h * img_w) if img_pad is None else img_pad
+    pos = np.zeros((img_h * img_w + img_pad + cap_total, 3), dtype=np.uintp)
+    lib().orc_zimage_positions(_p(pos), img_h, img_w, img_pad, cap_total)
     return pos
 
 

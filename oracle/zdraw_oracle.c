@@ -352,10 +352,14 @@ ORC_API int orc_zrope_apply(float *vec, const float *values, const size_t dims[3
  * Unified Z-Image sequence positions: image tokens first, caption tokens after
  * (zunify.zig:16-37). Caption token i has position (1+i, 0, 0) over the padded
  * caption length (zstreams.zig:112-130 with start (1,0,0), zstep_shape.zig:63-66);
- * image token (r, c) has (cap_total+1, r, c) (zstep_shape.zig:58-60). `pos`
- * receives [img_h*img_w + cap_total][3].
+ * image token (r, c) has (cap_total+1, r, c) (zstep_shape.zig:58-60). The image
+ * stream is padded to a multiple of 32 tokens (zstep_shape.zig:33-46, img_total =
+ * paddedLen(img_raw)) and its pad slots collapse to the origin (zseq.zig:55-61:
+ * "any slots past it collapse to the origin"). `pos` receives
+ * [img_h*img_w + img_pad + cap_total][3].
  */
-ORC_API void orc_zimage_positions(size_t *pos, size_t img_h, size_t img_w, size_t cap_total) {
+ORC_API void orc_zimage_positions(size_t *pos, size_t img_h, size_t img_w, size_t img_pad,
+                                  size_t cap_total) {
   size_t t = 0;
   for (size_t r = 0; r < img_h; ++r)
     for (size_t c = 0; c < img_w; ++c, ++t) {
@@ -363,6 +367,7 @@ ORC_API void orc_zimage_positions(size_t *pos, size_t img_h, size_t img_w, size_
       pos[3 * t + 1] = r;
       pos[3 * t + 2] = c;
     }
+  for (size_t i = 0; i < img_pad; ++i, ++t) pos[3 * t] = pos[3 * t + 1] = pos[3 * t + 2] = 0;
   for (size_t i = 0; i < cap_total; ++i, ++t) {
     pos[3 * t] = 1 + i;
     pos[3 * t + 1] = 0;

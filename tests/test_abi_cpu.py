@@ -62,6 +62,15 @@ def test_zimage_rope_table_matches_oracle(lib, oracle):
     want_c, want_s = oracle.zrope_expand(values, dims, lens, pos)
     np.testing.assert_array_equal(got_c, want_c)
     np.testing.assert_array_equal(got_s, want_s)
+    # An image stream that is not a multiple of 32 tokens (45 x 45 = 2025 -> 2048): pad slots at the origin
+    # (zseq.zig:36-61), i.e. cos 1 / sin 0, between the image rows and the caption rows.
+    got_c, got_s = mattn.zimage_rope_table(45, 45, 64, dims, lens, 256.0)
+    assert got_c.shape == (2048 + 64, 128)
+    pos = oracle.zimage_positions(45, 45, 64)
+    want_c, want_s = oracle.zrope_expand(values, dims, lens, pos)
+    np.testing.assert_array_equal(got_c, want_c)
+    np.testing.assert_array_equal(got_s, want_s)
+    assert (got_c[2025:2048] == 1.0).all() and (got_s[2025:2048] == 0.0).all()
     with pytest.raises(mattn.InvalidShape):  # caption position beyond the axis length
         mattn.zimage_rope_table(2, 2, 2000, dims, lens, 256.0)
     with pytest.raises(mattn.InvalidShape):  # odd axis dim

@@ -126,7 +126,7 @@ def test_klein_rope_table_ids(oracle):
 
 def test_zimage_positions_and_expand(oracle):
     # zunify.zig:31-34 image first; zstep_shape.zig:58-66 image at (cap_total+1, r, c), caption (1+i,0,0).
-    pos = oracle.zimage_positions(2, 3, 4)
+    pos = oracle.zimage_positions(2, 3, 4, img_pad=0)
     assert pos.shape == (10, 3)
     assert pos[0].tolist() == [5, 0, 0] and pos[5].tolist() == [5, 1, 2]
     assert pos[6].tolist() == [1, 0, 0] and pos[9].tolist() == [4, 0, 0]
@@ -140,6 +140,26 @@ def test_zimage_positions_and_expand(oracle):
         for h in range(2):
             want = oracle.zrope_apply(x[t, h], values, dims, lens, pos[t])
             np.testing.assert_array_equal(via_table[t, h], want)
+
+
+def test_zimage_image_pad_slots_sit_at_the_origin(oracle):
+    # zseq.zig:94-98: padLen(32) = 0, padLen(2) = 30, paddedLen(33) = 64.
+    assert [oracle.zimage_pad_len(n) for n in (32, 2, 33)] == [0, 30, 31]
+    # zseq.zig:113-127: a 1 x 2 grid starting at (7, 0, 0) padded to 32 slots has ids[1] = (7, 0, 1)
+    # and ids[2] = (0, 0, 0). With cap_total = 6 the image frame coordinate is cap_total + 1 = 7.
+    pos = oracle.zimage_positions(1, 2, 6)
+    assert pos.shape == (32 + 6, 3)
+    assert pos[1].tolist() == [7, 0, 1] and pos[2].tolist() == [0, 0, 0] and pos[31].tolist() == [0, 0, 0]
+    assert pos[32].tolist() == [1, 0, 0] and pos[37].tolist() == [6, 0, 0]
+    # zstep_shape.zig:108-128: 4 image patches -> img_total 32; the caption stream is padded by the caller
+    # (cap_total = 32 there) and keeps counting over its padding (zstep_shape.zig:63-66).
+    pos = oracle.zimage_positions(2, 2, 32)
+    assert pos.shape == (64, 3) and pos[3].tolist() == [33, 1, 1] and pos[4].tolist() == [0, 0, 0]
+    assert pos[32].tolist() == [1, 0, 0] and pos[63].tolist() == [32, 0, 0]
+    # A 45 x 45 grid: 2025 patches -> 2048 slots.
+    pos = oracle.zimage_positions(45, 45, 64)
+    assert pos.shape == (2048 + 64, 3)
+    assert pos[2024].tolist() == [65, 44, 44] and pos[2025].tolist() == [0, 0, 0] and pos[2048].tolist() == [1, 0, 0]
 
 
 def test_f32_oracle_close_to_f64_and_thread_invariant(oracle):

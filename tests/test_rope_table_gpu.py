@@ -40,7 +40,7 @@ def test_klein_table_equals_host_builder_bit_for_bit(ctx, txt, gh, gw, rh, rw, t
     assert np.array_equal(sin_d.cpu().numpy(), want_s)
 
 
-@pytest.mark.parametrize("h,w,cap", [(64, 64, 32), (3, 5, 7), (1, 1, 0), (0, 0, 9), (96, 64, 511 - 1)])
+@pytest.mark.parametrize("h,w,cap", [(64, 64, 32), (3, 5, 7), (1, 1, 0), (0, 0, 9), (96, 64, 511 - 1), (45, 45, 64)])
 def test_zimage_table_within_one_ulp_of_host_builder(ctx, h, w, cap):
     want_c, want_s = mattn.zimage_rope_table(h, w, cap)
     cos_d, sin_d = ctx.zimage_rope_table_device(h, w, cap)
@@ -53,6 +53,11 @@ def test_zimage_table_within_one_ulp_of_host_builder(ctx, h, w, cap):
         assert (d != 0).mean() < 0.05
         # Pair structure of the table: both columns of a pair hold the same value.
         assert np.array_equal(got[:, 0::2], got[:, 1::2])
+    # Image pad slots (the image stream padded to a multiple of 32 tokens) sit at the origin.
+    pad = mattn.zimage_pad_len(h * w)
+    assert cos_d.shape[0] == h * w + pad + cap
+    if pad:
+        assert bool((cos_d[h * w: h * w + pad] == 1.0).all()) and bool((sin_d[h * w: h * w + pad] == 0.0).all())
 
 
 def test_invalid_configurations_are_rejected_like_the_host_builders(ctx):

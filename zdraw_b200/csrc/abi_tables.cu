@@ -42,8 +42,8 @@ int zdraw_cuda_klein_rope_table(float* cos_out, float* sin_out, size_t txt_len, 
   return ZDRAW_CUDA_OK;
 }
 
-int zdraw_cuda_zimage_rope_table(float* cos_out, float* sin_out, size_t img_h, size_t img_w, size_t cap_total,
-                                 const size_t dims[3], const size_t lens[3], float theta) {
+int zdraw_cuda_zimage_rope_table(float* cos_out, float* sin_out, size_t img_h, size_t img_w, size_t img_pad,
+                                 size_t cap_total, const size_t dims[3], const size_t lens[3], float theta) {
   if (!cos_out || !sin_out || !dims || !lens) return ZDRAW_CUDA_E_ARG;
   if (!(theta > 0.0f)) return ZDRAW_CUDA_E_ARG;
   size_t width = 0;
@@ -54,14 +54,16 @@ int zdraw_cuda_zimage_rope_table(float* cos_out, float* sin_out, size_t img_h, s
   if (width != kHeadDim) return ZDRAW_CUDA_E_ARG;
   const size_t n_img = img_h * img_w;
   const float neg_log_theta = -std::log(theta);
-  for (size_t t = 0; t < n_img + cap_total; ++t) {
+  for (size_t t = 0; t < n_img + img_pad + cap_total; ++t) {
     size_t pos[3];
     if (t < n_img) {  // image tokens come first
       pos[0] = cap_total + 1;
       pos[1] = t / img_w;
       pos[2] = t % img_w;
+    } else if (t < n_img + img_pad) {  // image pad slots sit at the origin (zseq.zig:55-61)
+      pos[0] = pos[1] = pos[2] = 0;
     } else {
-      pos[0] = 1 + (t - n_img);
+      pos[0] = 1 + (t - n_img - img_pad);
       pos[1] = 0;
       pos[2] = 0;
     }
@@ -111,8 +113,8 @@ int zdraw_cuda_klein_rope_table_device(void* ctx, void* stream, float* cos_dev, 
 }
 
 int zdraw_cuda_zimage_rope_table_device(void* ctx, void* stream, float* cos_dev, float* sin_dev, size_t img_h,
-                                        size_t img_w, size_t cap_total, const size_t dims[3], const size_t lens[3],
-                                        float theta) {
+                                        size_t img_w, size_t img_pad, size_t cap_total, const size_t dims[3],
+                                        const size_t lens[3], float theta) {
   Ctx* c = as_ctx(ctx);
   if (!c) return ZDRAW_CUDA_E_ARG;
   if (!cos_dev || !sin_dev || !aligned16(cos_dev) || !aligned16(sin_dev) || !dims || !lens || !(theta > 0.0f))
@@ -123,7 +125,8 @@ int zdraw_cuda_zimage_rope_table_device(void* ctx, void* stream, float* cos_dev,
     width += dims[a];
   }
   if (width != kHeadDim) return fail(c, ZDRAW_CUDA_E_ARG, "InvalidConfig: axis sizes do not add up to 128");
-  if (img_h > kMaxTokens || img_w > kMaxTokens || cap_total > kMaxTokens || img_h * img_w + cap_total > kMaxTokens)
+  if (img_h > kMaxTokens || img_w > kMaxTokens || img_pad > kMaxTokens || cap_total > kMaxTokens ||
+      img_h * img_w + img_pad + cap_total > kMaxTokens)
     return fail(c, ZDRAW_CUDA_DECLINED, "more tokens than the attention kernels take");
   // BadPosition, as the host builder finds it token by token: the largest position on each axis.
   const size_t n_img = img_h * img_w;
@@ -135,8 +138,9 @@ int zdraw_cuda_zimage_rope_table_device(void* ctx, void* stream, float* cos_dev,
   a.sin_out = sin_dev;
   a.img_h = static_cast<int>(img_h);
   a.img_w = static_cast<int>(img_w);
+  a.img_pad = static_cast<int>(img_pad);
   a.cap_total = static_cast<int>(cap_total);
-  a.tokens = static_cast<int>(n_img + cap_total);
+  a.tokens = static_cast<int>(n_img + img_pad + cap_total);
   const float neg_log_theta = -std::log(theta);
   int pair = 0;
   for (int ax = 0; ax < 3; ++ax)

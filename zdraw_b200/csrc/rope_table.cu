@@ -55,8 +55,10 @@ __global__ void __launch_bounds__(256) zimage_rope_table_kernel(const ZimageRope
     pos[0] = a.cap_total + 1;
     pos[1] = t / a.img_w;
     pos[2] = t % a.img_w;
+  } else if (t < n_img + a.img_pad) {  // image pad slots sit at the origin
+    pos[0] = pos[1] = pos[2] = 0;
   } else {
-    pos[0] = 1 + (t - n_img);
+    pos[0] = 1 + (t - n_img - a.img_pad);
     pos[1] = 0;
     pos[2] = 0;
   }

@@ -17,11 +17,11 @@ struct KleinRopeArgs {
 };
 
 // Z-Image: 64 column pairs; pair p belongs to axis axis[p] and has frequency freq[p] (f32, computed
-// on the host as the host builder does); unified order is image tokens first, then caption.
+// on the host as the host builder does); unified order is image tokens, image pad slots, then caption.
 struct ZimageRopeArgs {
   float* cos_out;
   float* sin_out;
-  int img_h, img_w, cap_total;
+  int img_h, img_w, img_pad, cap_total;  // img_pad slots at position (0,0,0) follow the image tokens
   int tokens;
   float freq[64];
   unsigned char axis[64];

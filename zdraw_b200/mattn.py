@@ -228,19 +228,21 @@ class Context:
         return cos_t, sin_t
 
     def zimage_rope_table_device(self, img_h: int, img_w: int, cap_total: int, dims=(32, 48, 48),
-                                 lens=(1536, 512, 512), theta: float = 256.0, stream=None):
-        """``zrope.Cache`` gathered over [image | caption] (src/zimage/zrope.zig:32-116,
-        src/zimage/zunify.zig:16-37) on the GPU: cos, sin [tokens][128] f32 device tensors."""
+                                 lens=(1536, 512, 512), theta: float = 256.0, stream=None, img_pad=None):
+        """``zrope.Cache`` gathered over [image | image pad | caption] (src/zimage/zrope.zig:32-116,
+        src/zimage/zunify.zig:16-37, zseq.zig:36-61) on the GPU: cos, sin [tokens][128] f32 device
+        tensors. ``img_pad`` defaults to the reference's padding of the image stream to a multiple of 32."""
         import torch
 
-        tokens = img_h * img_w + cap_total
+        img_pad = zimage_pad_len(img_h * img_w) if img_pad is None else img_pad
+        tokens = img_h * img_w + img_pad + cap_total
         cos_t = torch.empty((tokens, HEAD_DIM), dtype=torch.float32, device=f"cuda:{self.device}")
         sin_t = torch.empty_like(cos_t)
         d = np.ascontiguousarray(dims, np.uintp)
         ln = np.ascontiguousarray(lens, np.uintp)
         self._check(self._lib.zdraw_cuda_zimage_rope_table_device(
-            self._h, self._stream_ptr(stream), _ptr(cos_t), _ptr(sin_t), img_h, img_w, cap_total, _ptr(d), _ptr(ln),
-            float(theta)))
+            self._h, self._stream_ptr(stream), _ptr(cos_t), _ptr(sin_t), img_h, img_w, img_pad, cap_total, _ptr(d),
+            _ptr(ln), float(theta)))
         return cos_t, sin_t
 
     def joint_attention_host(self, q, k, v, q_w_txt, q_w_img, k_w_txt, k_w_img, rope_cos, rope_sin, out,
@@ -266,17 +268,25 @@ def klein_rope_table(txt_len: int, grid_h: int, grid_w: int, ref_h: int = 0, ref
     return cos_t, sin_t
 
 
+def zimage_pad_len(tokens: int) -> int:
+    """``zseq.padLen`` (src/zimage/zseq.zig:15-17): slots that pad a stream to a multiple of 32."""
+    return (32 - tokens % 32) % 32
+
+
 def zimage_rope_table(img_h: int, img_w: int, cap_total: int, dims=(32, 48, 48), lens=(1536, 512, 512),
-                      theta: float = 256.0):
-    """``zrope.Cache`` gathered over the unified sequence [image | caption]
-    (src/zimage/zrope.zig:32-116, src/zimage/zunify.zig:16-37): cos, sin [tokens][128] f32."""
-    tokens = img_h * img_w + cap_total
+                      theta: float = 256.0, img_pad=None):
+    """``zrope.Cache`` gathered over the unified sequence [image | image pad | caption]
+    (src/zimage/zrope.zig:32-116, src/zimage/zunify.zig:16-37; pad slots at the origin,
+    zseq.zig:36-61): cos, sin [tokens][128] f32. ``img_pad`` defaults to the reference's padding of
+    the image stream to a multiple of 32."""
+    img_pad = zimage_pad_len(img_h * img_w) if img_pad is None else img_pad
+    tokens = img_h * img_w + img_pad + cap_total
     cos_t = np.empty((tokens, HEAD_DIM), np.float32)
     sin_t = np.empty((tokens, HEAD_DIM), np.float32)
     d = np.ascontiguousarray(dims, np.uintp)
     ln = np.ascontiguousarray(lens, np.uintp)
-    rc = _lib.lib().zdraw_cuda_zimage_rope_table(_ptr(cos_t), _ptr(sin_t), img_h, img_w, cap_total, _ptr(d), _ptr(ln),
-                                                 float(theta))
+    rc = _lib.lib().zdraw_cuda_zimage_rope_table(_ptr(cos_t), _ptr(sin_t), img_h, img_w, img_pad, cap_total, _ptr(d),
+                                                 _ptr(ln), float(theta))
     if rc != 0:
         raise InvalidShape("InvalidConfig or BadPosition")
     return cos_t, sin_t
