@@ -52,7 +52,28 @@ constexpr int kThreads = 384;
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 constexpr float kRescaleThreshold = 8.0f;                       // log2 units
 constexpr int kTraceIters = 40, kTraceEvents = 8;
-constexpr int kEmuPairsOf4 = 0;  // of every 4 score pairs, how many take the FMA-pipe exp2 (0..4)
+#ifndef ZD_EMU
+#define ZD_EMU 0
+#endif
+#ifndef ZD_FOLDMAX
+#define ZD_FOLDMAX 1
+#endif
+#ifndef ZD_HIDEPOLL
+#define ZD_HIDEPOLL 1
+#endif
+#ifndef ZD_PIECES
+#define ZD_PIECES 3
+#endif
+// P of a K/V step reaches the MMA warp in pieces, so that O += P V starts on the first keys while
+// the last ones are still being exponentiated. Piece ends in units of 16 keys (one MMA K-step):
+// 2 pieces {4, 8}, 3 pieces {4, 6, 8}, 4 pieces {2, 4, 6, 8}.
+constexpr int kPieces = ZD_PIECES;
+static_assert(kPieces >= 2 && kPieces <= 4, "piece count");
+__host__ __device__ constexpr int piece_end(int i) {
+  return kPieces == 2 ? 4 * (i + 1) : (kPieces == 3 ? (i == 0 ? 4 : (i == 1 ? 6 : 8)) : 2 * (i + 1));
+}
+__host__ __device__ constexpr int piece_begin(int i) { return i == 0 ? 0 : piece_end(i - 1); }
+constexpr int kEmuPairsOf4 = ZD_EMU;  // of every 4 score pairs, how many take the FMA-pipe exp2 (0..4)
 // Register budgets after setmaxnreg. The CTA is launched with 168 registers per thread
 // (3 warpgroups x 168 = 504 per lane triple); what the control warpgroup gives up is all the
 // softmax warpgroups can take, so kRegsControl + 2 * kRegsSoftmax must not exceed 504
@@ -71,10 +92,10 @@ constexpr int kBarQFull = 0;                      // [2]
 constexpr int kBarKVFull = 2;                     // [kStages]
 constexpr int kBarKVEmpty = 2 + kStages;          // [kStages]
 constexpr int kBarSFull = 2 + 2 * kStages;        // [2]
-constexpr int kBarPFull = 4 + 2 * kStages;        // [2 tiles][2 key halves]
-constexpr int kBarOFull = 8 + 2 * kStages;        // [2]
-constexpr int kBarDrain = 10 + 2 * kStages;       // [1]
-constexpr int kNumBars = 11 + 2 * kStages;
+constexpr int kBarPFull = 4 + 2 * kStages;        // [2 tiles][kPieces]
+constexpr int kBarOFull = kBarPFull + 2 * kPieces;  // [2]
+constexpr int kBarDrain = kBarOFull + 2;          // [1]
+constexpr int kNumBars = kBarDrain + 1;
 constexpr int kOffFlags = kOffBar + kNumBars * 8;  // u32 abort, u32 tmem base
 constexpr int kSmemBytes = kOffFlags + 16 + 1024;  // + alignment slack
 
@@ -189,8 +210,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar(kBarSFull + t), 1);
-      mbar_init(bar(kBarPFull + 2 * t), kBM);
-      mbar_init(bar(kBarPFull + 2 * t + 1), kBM);
+      for (int i = 0; i < kPieces; ++i) mbar_init(bar(kBarPFull + kPieces * t + i), kBM);
       mbar_init(bar(kBarOFull + t), 1);
     }
     mbar_init(bar(kBarDrain), 1);
@@ -212,6 +232,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // Everything above overlaps the tail of the preceding kernel (the prologue) when the launch
   // allows it; from here on this kernel reads what earlier kernels wrote.
   grid_dependency_wait();
+  if (kTrace && tracing && threadIdx.x == 0) {
+    // SM clock and wall clock at the start of the CTA's work (role 3, step 0, events 4 and 5).
+    a.trace[(3 * kTraceIters) * kTraceEvents + 4] = static_cast<unsigned long long>(clock64());
+    a.trace[(3 * kTraceIters) * kTraceEvents + 5] = globaltimer_ns();
+  }
 
   // Coordinates of (token row, head) in the two tensor-map dimension orders.
   auto c1 = [&](int hm, int tok) { return hm ? tok : head; };
@@ -252,6 +277,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           stamp(3, i, 1);
           const uint32_t dst = base + kOffKV + slot * 2 * kTileBytes;
           const bool has_v = i >= 1, has_k = i < n_act;
+#ifdef ZD_ABLATE_HALFLOAD  // timing experiment only (wrong results): half of the K/V bytes are fetched
+          mbar_arrive_expect_tx(bar(kBarKVFull + slot), (has_v ? kHalfBytes : 0) + (has_k ? kHalfBytes : 0));
+          if (has_v) {
+            const int row = (tile_entry(i - 1) & kTileIndexMask) * kBN;
+            const int hm = a.v_head_major;
+            tma_load_4d(dst, &tm_v, bar(kBarKVFull + slot), 0, c1(hm, row), c2(hm, row), img);
+          }
+          if (has_k) {
+            const int row = (tile_entry(i) & kTileIndexMask) * kBN;
+            const int hm = a.k_head_major;
+            tma_load_4d(dst + kTileBytes, &tm_k, bar(kBarKVFull + slot), 0, c1(hm, row), c2(hm, row), img);
+          }
+#else
           mbar_arrive_expect_tx(bar(kBarKVFull + slot), (has_v ? kTileBytes : 0) + (has_k ? kTileBytes : 0));
           if (has_v) {
             const int row = (tile_entry(i - 1) & kTileIndexMask) * kBN;
@@ -265,6 +303,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tma_load_4d(dst + kTileBytes, &tm_k, bar(kBarKVFull + slot), 0, c1(hm, row), c2(hm, row), img);
             tma_load_4d(dst + kTileBytes + kHalfBytes, &tm_k, bar(kBarKVFull + slot), 64, c1(hm, row), c2(hm, row), img);
           }
+#endif
         }
         if (!ok) {
           // Let copies that are still in flight land before the CTA's shared memory goes away.
@@ -292,15 +331,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         };
         // O_t (+)= P_t V: the K dimension is 128 keys = 8 steps of 16 keys (2048 bytes of V
         // rows, 8 TMEM columns of packed f16 P); N = head_dim spans two 64-column blocks (LBO).
-        // `half` selects keys [0,64) or [64,128) of the tile: the softmax warps hand P over in two
-        // pieces so that the first four MMAs run while the second half is still being exponentiated.
-        auto issue_pv = [&](int t, uint32_t v_addr, int half, bool accumulate) {
+        // Steps [k0, k1) belong to one piece of P: the softmax warps hand P over in pieces so that
+        // the first MMAs run while the last keys are still being exponentiated.
+        auto issue_pv = [&](int t, uint32_t v_addr, int k0, int k1, bool accumulate) {
           const uint64_t desc_v = smem_desc_sw128(v_addr, kHalfBytes, 1024);
           const uint32_t p_tmem = tmem_base + 128u * t;
           const uint32_t d_tmem = tmem_base + 256u + 128u * t;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const int k = 4 * half + kk;
+          for (int k = k0; k < k1; ++k) {
             umma_ts(d_tmem, p_tmem + 8u * k, desc_v + ((2048u * k) >> 4), idesc_pv,
                     (accumulate || k > 0) ? 1u : 0u);
           }
@@ -318,9 +356,82 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_commit(bar(kBarSFull + 1));
           umma_commit(bar(kBarKVEmpty + 0));
         }
+#if ZD_HIDEPOLL
+        // Steps with a successor: every barrier the next batch of MMAs depends on is probed
+        // ahead of the current batch (inside its asm block), so a probe that finds the phase
+        // complete costs the tensor pipe nothing; one that does not falls back to a wait.
+        // (The instrumented copy of the kernel takes the plain path for every step: that path
+        // carries the time stamps.)
+        uint32_t rdy_kv = 0, rdy_p = 0;
+        int jj0 = 0;
+        for (; !kTrace && jj0 + 1 < n_act && ok; ++jj0) {
+          const uint32_t pair = static_cast<uint32_t>(jj0) + 1u;
+          const uint32_t slot = pair % kPairStages;
+          const uint32_t par = static_cast<uint32_t>(jj0) & 1u;
+          if (!rdy_kv) ok = wait_bar(bar(kBarKVFull + slot), (pair / kPairStages) & 1u, abort_flag, a.status, kStMma);
+          if (ok && !rdy_p) ok = wait_bar(bar(kBarPFull + 0), par, abort_flag, a.status, kStMma);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t v_addr = base + kOffKV + slot * 2 * kTileBytes;
+          const uint64_t desc_v = smem_desc_sw128(v_addr, kHalfBytes, 1024);
+          const uint64_t desc_k = smem_desc_sw128(v_addr + kTileBytes, 16, 1024);
+          const uint32_t acc = jj0 > 0 ? 1u : 0u;
+          const uint32_t npair = pair + 1u, nslot = npair % kPairStages;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const uint32_t p_tmem = tmem_base + 128u * t, d_tmem = tmem_base + 256u + 128u * t;
+            const uint64_t desc_q = smem_desc_sw128(base + kOffQ + t * kTileBytes, 16, 1024);
+#pragma unroll
+            for (int i = 0; i < kPieces; ++i) {
+              const int k0 = piece_begin(i), n = piece_end(i) - piece_begin(i);
+              const uint32_t pa = p_tmem + 8u * k0;
+              const uint64_t dv = desc_v + 128u * k0;
+              if (i + 1 < kPieces) {
+                // The next piece of this tile's P is probed ahead of this piece's MMAs.
+                const uint32_t nb = bar(kBarPFull + kPieces * t + i + 1);
+                const uint32_t r = (n == 4) ? umma_ts4_probe(d_tmem, pa, dv, idesc_pv, (i == 0) ? acc : 1u, nb, par)
+                                            : umma_ts2_probe(d_tmem, pa, dv, idesc_pv, (i == 0) ? acc : 1u, nb, par);
+                if (!r) {
+                  ok = wait_bar(nb, par, abort_flag, a.status, kStMma);
+                  if (!ok) break;
+                }
+                tc_fence_after();
+              } else if (t == 0) {
+                // Last piece and the next Q K^T; probed: the first piece of tile 1 (this step).
+                const uint32_t nb = bar(kBarPFull + kPieces);
+                uint32_t r1, r2;
+                if (n == 4) umma_ts4_ss8_probe2(d_tmem, pa, dv, idesc_pv, p_tmem, desc_q, desc_k, idesc_qk, nb, par, nb, par, r1, r2);
+                else umma_ts2_ss8_probe2(d_tmem, pa, dv, idesc_pv, p_tmem, desc_q, desc_k, idesc_qk, nb, par, nb, par, r1, r2);
+                umma_commit(bar(kBarSFull + 0));
+                if (!r1) {
+                  ok = wait_bar(nb, par, abort_flag, a.status, kStMma);
+                  if (!ok) break;
+                }
+                tc_fence_after();
+              } else {
+                // Probed: the following pair of the ring and the first piece of tile 0 (next step).
+                if (n == 4)
+                  umma_ts4_ss8_probe2(d_tmem, pa, dv, idesc_pv, p_tmem, desc_q, desc_k, idesc_qk, bar(kBarKVFull + nslot),
+                                      (npair / kPairStages) & 1u, bar(kBarPFull + 0), par ^ 1u, rdy_kv, rdy_p);
+                else
+                  umma_ts2_ss8_probe2(d_tmem, pa, dv, idesc_pv, p_tmem, desc_q, desc_k, idesc_qk, bar(kBarKVFull + nslot),
+                                      (npair / kPairStages) & 1u, bar(kBarPFull + 0), par ^ 1u, rdy_kv, rdy_p);
+                umma_commit(bar(kBarSFull + 1));
+              }
+            }
+            if (!ok) break;
+          }
+          if (!ok) break;
+          umma_commit(bar(kBarKVEmpty + slot));
+        }
+        // The last step (or the only one) takes the plain path below; what was probed for it counts.
+        for (int jj = jj0; jj < n_act && ok; ++jj) {
+          const uint32_t pair = static_cast<uint32_t>(jj) + 1u;
+#else
         for (int jj = 0; jj < n_act && ok; ++jj) {
           // Pair jj + 1: V of this step's tile and K of the next step's.
           const uint32_t pair = static_cast<uint32_t>(jj) + 1u;
+#endif
           const uint32_t slot = pair % kPairStages;
           stamp(4, jj, 0);
           ok = wait_bar(bar(kBarKVFull + slot), (pair / kPairStages) & 1u, abort_flag, a.status, kStMma);
@@ -334,16 +445,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int t = 0; t < 2; ++t) {
             stamp(0, jj, 4 * t + 0);
-            ok = wait_bar(bar(kBarPFull + 2 * t), static_cast<uint32_t>(jj) & 1u, abort_flag, a.status, kStMma);
+#pragma unroll
+            for (int i = 0; i < kPieces; ++i) {
+              ok = wait_bar(bar(kBarPFull + kPieces * t + i), static_cast<uint32_t>(jj) & 1u, abort_flag, a.status, kStMma);
+              if (!ok) break;
+              tc_fence_after();
+              if (i < 2) stamp(0, jj, 4 * t + 1 + i);
+              issue_pv(t, v_addr, piece_begin(i), piece_end(i), jj > 0);
+            }
             if (!ok) break;
-            tc_fence_after();
-            stamp(0, jj, 4 * t + 1);
-            issue_pv(t, v_addr, 0, jj > 0);
-            ok = wait_bar(bar(kBarPFull + 2 * t + 1), static_cast<uint32_t>(jj) & 1u, abort_flag, a.status, kStMma);
-            if (!ok) break;
-            tc_fence_after();
-            stamp(0, jj, 4 * t + 2);
-            issue_pv(t, v_addr, 1, jj > 0);
             if (has_next) {
               issue_qk(t, k_addr);
               umma_commit(bar(kBarSFull + t));
@@ -428,6 +538,109 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int i = 0; i < 128; ++i) s[i] = (i < tail) ? s[i] : -INFINITY;
       }
 
+#if ZD_FOLDMAX
+      // The row maximum is taken off the chain S -> P: the exponentials of the first 64 keys are
+      // computed against the running maximum m of the steps before, while the maximum of all 128
+      // new scores is reduced beside them (the exponentials keep the MUFU busy, the reduction
+      // runs on the ALU). Only when the new maximum exceeds m by more than the lazy-rescale
+      // bound - a property of the data alone - are O and l rescaled and those exponentials
+      // redone. Nothing of this step has been handed to the MMA warp before that decision.
+      auto row_max = [&]() -> float {
+        float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+        float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
+#pragma unroll
+        for (int i = 12; i < 124; i += 8) {
+          mx0 = max3(mx0, s[i], s[i + 1]);
+          mx1 = max3(mx1, s[i + 2], s[i + 3]);
+          mx2 = max3(mx2, s[i + 4], s[i + 5]);
+          mx3 = max3(mx3, s[i + 6], s[i + 7]);
+        }
+        mx0 = max3(mx0, s[124], s[125]);
+        mx1 = max3(mx1, s[126], s[127]);
+        return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      };
+      const uint64_t c2 = f2_pack(c, c);
+      uint64_t acc0 = 0ull, acc1 = 0ull;  // packed partial row sums (+0.0f, +0.0f)
+      // 32 scores -> 16 packed f16x2 words of P, partial sums into acc0/acc1.
+      auto exp_chunk = [&](int ch, uint64_t nmc2, uint32_t* pk) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int e = 32 * ch + 2 * i;
+          const uint64_t x2 = f2_fma(f2_pack(s[e], s[e + 1]), c2, nmc2);
+          uint64_t p2;
+          if ((i & 3) < kEmuPairsOf4) {
+            p2 = exp2_emulated_pair(x2);
+          } else {
+            float x0, x1;
+            f2_unpack(x2, x0, x1);
+            p2 = f2_pack(ex2_approx(x0), ex2_approx(x1));
+          }
+          if (i & 1) acc1 = f2_add(acc1, p2); else acc0 = f2_add(acc0, p2);
+          float p0, p1;
+          f2_unpack(p2, p0, p1);
+          pk[i] = pack_f16x2(p0, p1);
+        }
+      };
+      if (jj == 0) m = row_max();  // the first tile has no earlier maximum to lean on
+      float mc = (m == -INFINITY) ? 0.0f : m * c;
+      uint64_t nmc2 = f2_pack(-mc, -mc);
+      uint32_t pk0[16], pk1[16];
+      exp_chunk(0, nmc2, pk0);
+      exp_chunk(1, nmc2, pk1);
+      {
+        const float m_row = row_max();
+        const bool need = (m_row - m) * c > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          // PV of the previous step has completed: the commit that released S covers it.
+          float alpha = 1.0f;
+          if (need) {
+            alpha = ex2_approx((m - m_row) * c);
+            m = m_row;
+          }
+          l *= alpha;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t o[32];
+            tmem_ld_x32(t_o + 32u * ch, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_x32(t_o + 32u * ch, o);
+          }
+          tmem_wait_st();
+          mc = (m == -INFINITY) ? 0.0f : m * c;
+          nmc2 = f2_pack(-mc, -mc);
+          acc0 = acc1 = 0ull;
+          exp_chunk(0, nmc2, pk0);
+          exp_chunk(1, nmc2, pk1);
+        }
+      }
+      if (tr) stamp(1 + t, jj, 3);
+      // Chunk ch holds keys [32 ch, 32 ch + 32) = MMA K-steps 2 ch and 2 ch + 1; a piece of P is
+      // handed over as soon as its last chunk has been stored.
+      auto publish = [&](int ch) {
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+          if (piece_end(i) == 2 * (ch + 1)) {
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(kBarPFull + kPieces * t + i));
+          }
+        }
+      };
+      tmem_st_x16(t_s + 0u, pk0);
+      publish(0);
+      tmem_st_x16(t_s + 16u, pk1);
+      publish(1);
+      if (tr) stamp(1 + t, jj, 4);
+      exp_chunk(2, nmc2, pk0);
+      tmem_st_x16(t_s + 32u, pk0);
+      publish(2);
+      exp_chunk(3, nmc2, pk1);
+      tmem_st_x16(t_s + 48u, pk1);
+      publish(3);
+      if (tr) stamp(1 + t, jj, 5);
+#else
       float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
       float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
 #pragma unroll
@@ -500,15 +713,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             pk[i] = pack_f16x2(p0, p1);
           }
           tmem_st_x16(t_s + 16u * ch, pk);
-          if (ch == 1 || ch == 3) {
-            // Keys [0,64) then [64,128) of P are handed to the MMA warp separately.
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(kBarPFull + 2 * t + (ch >> 1)));
-            if (tr) stamp(1 + t, jj, 4 + (ch >> 1));
+          // Chunk ch holds MMA K-steps 2 ch and 2 ch + 1: a piece of P is handed to the MMA warp as
+          // soon as its last chunk has been stored.
+#pragma unroll
+          for (int i = 0; i < kPieces; ++i) {
+            if (piece_end(i) == 2 * (ch + 1)) {
+              tmem_wait_st();
+              tc_fence_before();
+              mbar_arrive(bar(kBarPFull + kPieces * t + i));
+            }
           }
+          if (tr && (ch == 1 || ch == 3)) stamp(1 + t, jj, 4 + (ch >> 1));
         }
       }
+#endif
       {
         float a0, a1, b0, b1;
         f2_unpack(acc0, a0, a1);
@@ -580,6 +798,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
+  if (kTrace && tracing && threadIdx.x == 0) {
+    // ... and at its end (events 6 and 7): their ratio is the SM clock the CTA ran at.
+    a.trace[(3 * kTraceIters) * kTraceEvents + 6] = static_cast<unsigned long long>(clock64());
+    a.trace[(3 * kTraceIters) * kTraceEvents + 7] = globaltimer_ns();
+  }
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 

@@ -147,6 +147,168 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                : "memory");
 }
 
+// Batches of MMAs in one asm block with an mbarrier probe issued ahead of them: the probe's
+// result (has the phase `parity` of `bar` completed?) is read only after the MMAs have been
+// issued, so its latency (about a hundred clocks) overlaps their issue instead of leaving the
+// tensor pipe idle. A true result stays true until this thread lets the barrier move on.
+// Four O (+)= P V steps of 16 keys: P at a_tmem + 8 i, V rows at b_desc + 128 i (i = 0..3).
+__device__ __forceinline__ uint32_t umma_ts4_probe(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t accumulate_first, uint32_t bar, uint32_t parity) {
+  uint32_t ready;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pw, pa, pt;\n\t"
+      ".reg .b64 d1, d2, d3;\n\t"
+      ".reg .b32 a1, a2, a3;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pw, [%6], %7;\n\t"
+      "setp.ne.b32 pa, %5, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "add.u64 d1, %3, 128;\n\t"
+      "add.u64 d2, %3, 256;\n\t"
+      "add.u64 d3, %3, 384;\n\t"
+      "add.u32 a1, %2, 8;\n\t"
+      "add.u32 a2, %2, 16;\n\t"
+      "add.u32 a3, %2, 24;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %4, pa;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], d1, %4, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a2], d2, %4, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a3], d3, %4, pt;\n\t"
+      "selp.u32 %0, 1, 0, pw;\n\t"
+      "}"
+      : "=r"(ready)
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(bar), "r"(parity)
+      : "memory");
+  return ready;
+}
+// Four accumulating P V steps as above, then the eight K-steps of S = Q K^T for 128-wide
+// K-major operands (two 64-column blocks 16384 bytes apart); two barriers are probed ahead of
+// the twelve MMAs.
+__device__ __forceinline__ void umma_ts4_ss8_probe2(uint32_t d_o, uint32_t a_tmem, uint64_t v_desc, uint32_t idesc_pv,
+                                                    uint32_t d_s, uint64_t q_desc, uint64_t k_desc, uint32_t idesc_qk,
+                                                    uint32_t bar1, uint32_t parity1, uint32_t bar2, uint32_t parity2,
+                                                    uint32_t& ready1, uint32_t& ready2) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pw1, pw2, pt, pf;\n\t"
+      ".reg .b64 d1, d2, d3, q1, k1;\n\t"
+      ".reg .b32 a1, a2, a3;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pw1, [%10], %11;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pw2, [%12], %13;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "setp.ne.b32 pf, 0, 0;\n\t"
+      "add.u64 d1, %4, 128;\n\t"
+      "add.u64 d2, %4, 256;\n\t"
+      "add.u64 d3, %4, 384;\n\t"
+      "add.u32 a1, %3, 8;\n\t"
+      "add.u32 a2, %3, 16;\n\t"
+      "add.u32 a3, %3, 24;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], [%3], %4, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], [a1], d1, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], [a2], d2, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], [a3], d3, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], %7, %8, %9, pf;\n\t"
+      "add.u64 q1, %7, 2;\n\t"
+      "add.u64 k1, %8, 2;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 4;\n\t"
+      "add.u64 k1, %8, 4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 6;\n\t"
+      "add.u64 k1, %8, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 1024;\n\t"
+      "add.u64 k1, %8, 1024;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 1026;\n\t"
+      "add.u64 k1, %8, 1026;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 1028;\n\t"
+      "add.u64 k1, %8, 1028;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 1030;\n\t"
+      "add.u64 k1, %8, 1030;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "selp.u32 %0, 1, 0, pw1;\n\t"
+      "selp.u32 %1, 1, 0, pw2;\n\t"
+      "}"
+      : "=r"(ready1), "=r"(ready2)
+      : "r"(d_o), "r"(a_tmem), "l"(v_desc), "r"(idesc_pv), "r"(d_s), "l"(q_desc), "l"(k_desc), "r"(idesc_qk),
+        "r"(bar1), "r"(parity1), "r"(bar2), "r"(parity2)
+      : "memory");
+}
+
+// The same with two P V steps (i = 0, 1).
+__device__ __forceinline__ uint32_t umma_ts2_probe(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t accumulate_first, uint32_t bar, uint32_t parity) {
+  uint32_t ready;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pw, pa, pt;\n\t"
+      ".reg .b64 d1, d2, d3;\n\t"
+      ".reg .b32 a1, a2, a3;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pw, [%6], %7;\n\t"
+      "setp.ne.b32 pa, %5, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "add.u64 d1, %3, 128;\n\t"
+      "add.u32 a1, %2, 8;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [%2], %3, %4, pa;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%1], [a1], d1, %4, pt;\n\t"
+      "selp.u32 %0, 1, 0, pw;\n\t"
+      "}"
+      : "=r"(ready)
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(bar), "r"(parity)
+      : "memory");
+  return ready;
+}
+// Two accumulating P V steps, then the eight K-steps of S = Q K^T; two barriers probed ahead.
+__device__ __forceinline__ void umma_ts2_ss8_probe2(uint32_t d_o, uint32_t a_tmem, uint64_t v_desc, uint32_t idesc_pv,
+                                                    uint32_t d_s, uint64_t q_desc, uint64_t k_desc, uint32_t idesc_qk,
+                                                    uint32_t bar1, uint32_t parity1, uint32_t bar2, uint32_t parity2,
+                                                    uint32_t& ready1, uint32_t& ready2) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pw1, pw2, pt, pf;\n\t"
+      ".reg .b64 d1, d2, d3, q1, k1;\n\t"
+      ".reg .b32 a1, a2, a3;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pw1, [%10], %11;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pw2, [%12], %13;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "setp.ne.b32 pf, 0, 0;\n\t"
+      "add.u64 d1, %4, 128;\n\t"
+      "add.u32 a1, %3, 8;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], [%3], %4, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], [a1], d1, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], %7, %8, %9, pf;\n\t"
+      "add.u64 q1, %7, 2;\n\t"
+      "add.u64 k1, %8, 2;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 4;\n\t"
+      "add.u64 k1, %8, 4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 6;\n\t"
+      "add.u64 k1, %8, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 1024;\n\t"
+      "add.u64 k1, %8, 1024;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 1026;\n\t"
+      "add.u64 k1, %8, 1026;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 1028;\n\t"
+      "add.u64 k1, %8, 1028;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "add.u64 q1, %7, 1030;\n\t"
+      "add.u64 k1, %8, 1030;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%6], q1, k1, %9, pt;\n\t"
+      "selp.u32 %0, 1, 0, pw1;\n\t"
+      "selp.u32 %1, 1, 0, pw2;\n\t"
+      "}"
+      : "=r"(ready1), "=r"(ready2)
+      : "r"(d_o), "r"(a_tmem), "l"(v_desc), "r"(idesc_pv), "r"(d_s), "l"(q_desc), "l"(k_desc), "r"(idesc_qk),
+        "r"(bar1), "r"(parity1), "r"(bar2), "r"(parity2)
+      : "memory");
+}
+
 // Tile store shared -> global through a tensor map (completion tracked by bulk groups of the
 // issuing thread). x is the innermost coordinate: x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
