@@ -51,6 +51,17 @@ def measured_peaks():
     return dict(FALLBACK_PEAKS) | {"source": "fallback"}
 
 
+def captured_traffic(kernel: str, workload: str):
+    """DRAM bytes (read + write) per launch of `kernel` on `workload` from one ncu capture, or None."""
+    path = os.path.join(ROOT, "profiles", "counters.json")
+    try:
+        with open(path) as f:
+            c = json.load(f)[kernel][workload]
+        return float(c["dram_bytes_read"]) + float(c["dram_bytes_write"])
+    except (OSError, KeyError, ValueError):
+        return None
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU while the timed regions run."""
 
@@ -103,6 +114,41 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(s)}
 
 
+def oracle_inputs(w):
+    """Seeded inputs of one image of workload `w` for the CPU arm, made with numpy and the oracle's own
+    table builders (the product library is not loaded): same shapes and distributions as
+    `workloads.make_inputs` - q, k, v ~ N(0,1) rounded to the I/O dtype, weights ~ U(0.8, 1.2)."""
+    import numpy as np
+
+    import oracle
+
+    rng = np.random.default_rng(w.seed)
+    shape = (w.tokens, w.heads, 128)
+    h = {}
+    for name in ("q", "k", "v"):
+        t = rng.standard_normal(shape, dtype=np.float32)
+        h[name] = t if w.dtype == "f32" else t.astype(np.float16).astype(np.float32)
+    for name in ("q_w_txt", "q_w_img", "k_w_txt", "k_w_img"):
+        h[name] = np.ones(128, np.float32) if w.unit_weights else (rng.random(128, dtype=np.float32) * 0.4 + 0.8)
+    if w.family == "klein":
+        h["rope_cos"], h["rope_sin"] = oracle.klein_build_rope(w.txt_len, w.grid_h, w.grid_w, w.ref_h, w.ref_w, w.theta)
+    else:
+        dims, lens = [32, 48, 48], [1536, 512, 512]
+        pos = oracle.zimage_positions(w.grid_h, w.grid_w, w.txt_len)
+        h["rope_cos"], h["rope_sin"] = oracle.zrope_expand(oracle.zrope_fill(dims, lens, w.theta), dims, lens, pos)
+    h["key_mask"] = None
+    if w.masked_text is not None:
+        m = np.zeros(w.tokens, np.float32)
+        m[w.masked_text[0]:w.masked_text[1]] = -np.inf
+        h["key_mask"] = m
+    return h
+
+
+def workload_config(w, batch_per_gpu: int) -> dict:
+    """The `config` keys both arms share."""
+    return {"workload": w.name, "batch_per_gpu": batch_per_gpu, "heads": w.heads, "tokens": w.tokens, "head_dim": 128}
+
+
 class OracleTimer:
     """Times the CPU oracle's joint attention on a range of query rows of one image.
 
@@ -113,19 +159,17 @@ class OracleTimer:
 
     def __init__(self, w):
         import oracle
-        from zdraw_b200 import workloads
 
         self.oracle = oracle
         self.w = w.with_batch(1)
-        x = workloads.make_inputs(self.w, "cpu")
-        self.h = {k: (v.float().numpy() if v is not None else None) for k, v in x.items()}
+        self.h = oracle_inputs(self.w)
         self.norm_kind = 0 if w.family == "klein" else 1
 
     def run(self, rows: int) -> float:
         h, w = self.h, self.w
         b0 = (w.tokens - rows) // 2
         t0 = time.perf_counter()
-        self.oracle.joint_attention(h["q"][0], h["k"][0], h["v"][0], h["q_w_txt"], h["q_w_img"], h["k_w_txt"],
+        self.oracle.joint_attention(h["q"], h["k"], h["v"], h["q_w_txt"], h["q_w_img"], h["k_w_txt"],
                                     h["k_w_img"], h["rope_cos"], h["rope_sin"], w.heads, w.txt_tokens,
                                     self.norm_kind, w.eps, key_mask=h["key_mask"], rows=(b0, b0 + rows))
         return time.perf_counter() - t0
@@ -151,15 +195,21 @@ def run_reference(args, rank: int):
     if rank != 0:
         return
     import oracle
-    from zdraw_b200 import workloads
+    from zdraw_b200 import workloads  # shapes only: nothing here loads the CUDA library
 
     w = workloads.WORKLOADS[args.workload]
     oracle.build()
     cores = oracle.use_all_cores()
     timer = OracleTimer(w)
-    # Size a step to about 2 s of CPU work, bounded so that the whole run stays within minutes.
-    budget = min(2.0, 120.0 / max(args.steps + args.warmup, 1))
-    rows = timer.rows_for(budget)
+    # A step is a whole call when the run then stays within about ten minutes; else a bounded sample
+    # of query rows (work per row is uniform), extrapolated linearly.
+    per_row = timer.calibrate()
+    n_calls = max(args.steps + args.warmup, 1)
+    full_s = timer.overhead + w.tokens * per_row
+    if full_s * n_calls <= 600.0:
+        rows = w.tokens
+    else:
+        rows = int(max(8, min(w.tokens, (600.0 / n_calls - timer.overhead) / per_row)))
     for _ in range(args.warmup):
         timer.run(rows)
     t_total, vals = 0.0, []
@@ -168,19 +218,146 @@ def run_reference(args, rank: int):
         vals.append(timer.tflops(rows, dt))
         t_total += dt
     value = sum(vals) / len(vals)
-    sample = f"{rows} of {w.tokens} query rows x all {w.heads} heads of one image per step, all keys; extrapolated linearly in rows"
+    if rows == w.tokens:
+        sample = f"whole calls: all {w.tokens} query rows x all {w.heads} heads of one image per step, all keys"
+    else:
+        sample = (f"{rows} of {w.tokens} query rows x all {w.heads} heads of one image per step, all keys; "
+                  "extrapolated linearly in rows")
     line = {
         "impl": "reference", "metric": "attention TFLOP/s", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * w.with_batch(1).flops / (value * 1e12), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "batch": 1, "heads": w.heads, "tokens": w.tokens, "head_dim": 128,
-                   "note": "reference CPU path restated in C (oracle port); the reference itself is Zig + Metal"},
+        "config": workload_config(w, 1) | {
+            "note": "reference CPU path restated in C (oracle port); the reference itself is Zig + Metal"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def strong_scaling_record(ctx, rank, world, steps, warmup, stream, barrier, peaks):
+    """The metric call itself (klein_1024, one image) with its heads split over the ranks.
+
+    Every rank holds the same inputs (same seed) and computes heads [h0, h1). Timed, max over ranks:
+    the shard step without any exchange; with the gather of O done by the attention epilogue (plain
+    stores into every rank's buffer, then a one-element all-reduce as the fence that says all ranks
+    are done); and with one NCCL all-gather after the kernel, for comparison. The gathered O of
+    every rank is compared byte for byte with a 1-GPU run of the whole call on that rank: a mismatch
+    ends the run. `t1` is that 1-GPU run timed on rank 0 while the other ranks are idle.
+    """
+    import torch
+    import torch.distributed as dist
+
+    from zdraw_b200 import shard as shardlib
+    from zdraw_b200 import workloads
+
+    w = workloads.WORKLOADS["klein_1024"]
+    hs = shardlib.split(w.heads, world, rank)
+    shards = shardlib.all_shards(w.heads, world)
+    ld = w.heads * 128
+    p_shard = workloads.params(w, heads=hs.count, ld_q=ld, ld_k=ld, ld_v=ld, out_layout=1)
+    p_full = workloads.params(w, out_layout=1)
+    ctx.reserve(p_full)
+    x0 = workloads.make_inputs(w, "cuda")
+    shard_bytes = 4 * w.tokens * hs.count * 128 * 2
+    n_sets = min(24, max(2, int(2 * L2_BYTES // shard_bytes) + 1))
+    sets = [x0] + [{k: (v.clone() if k in ("q", "k", "v") else v) for k, v in x0.items()} for _ in range(n_sets - 1)]
+    hsl = slice(hs.begin, hs.end)
+    local = torch.empty((1, hs.count, w.tokens, 128), dtype=torch.float16, device="cuda")
+    full = torch.empty((1, w.heads, w.tokens, 128), dtype=torch.float16, device="cuda")
+    pg = shardlib.PeerGather(ctx, 1, w.heads, w.tokens, rank, world)
+
+    def shard_step(i):
+        x = sets[i % n_sets]
+        ctx.joint_attention(x["q"][:, :, hsl], x["k"][:, :, hsl], x["v"][:, :, hsl], x["q_w_txt"], x["q_w_img"],
+                            x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"], local, p_shard, stream=stream)
+
+    def full_step(i):
+        x = sets[i % n_sets]
+        ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                            x["rope_cos"], x["rope_sin"], full, p_full, stream=stream)
+
+    def timed(fn, sync_ranks=True):
+        for i in range(max(3, warmup)):
+            fn(i)
+        barrier() if sync_ranks else torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for i in range(steps):
+            fn(i)
+        b.record(stream)
+        barrier() if sync_ranks else torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    # 1 GPU, whole call: rank 0 alone (the others wait at the barrier below).
+    ms_1 = timed(full_step, sync_ranks=False) if rank == 0 else 0.0
+    barrier()
+    ms_plain = timed(shard_step)
+
+    def gather_step(i):
+        shard_step(i)
+        pg.fence()
+
+    ctx.set_gather(pg.targets, w.heads, hs.begin)
+    ms_peer = timed(gather_step)
+    # Byte check of the peer-store gather against this rank's own 1-GPU run of the same inputs.
+    pg.local.view(torch.uint8).fill_(0xFF)
+    barrier()
+    gather_step(0)
+    ctx.set_gather(None)
+    full_step(0)
+    barrier()
+    same_peer = bool(torch.equal(pg.local.view(torch.int16), full.view(torch.int16)))
+
+    def nccl_step(i):
+        shard_step(i)
+        return shardlib.all_gather_heads(local[0], w.heads, rank, world)
+
+    ms_nccl = timed(nccl_step)
+    same_nccl = bool(torch.equal(nccl_step(0).view(torch.int16), full[0].view(torch.int16)))
+
+    # the attention kernel alone on the shard
+    q16 = torch.empty((1, hs.count, w.tokens, 128), dtype=torch.float16, device="cuda")
+    k16 = torch.empty_like(q16)
+    ctx.qk_norm_rope(x0["q"][:, :, hsl], x0["k"][:, :, hsl], x0["q_w_txt"], x0["q_w_img"], x0["k_w_txt"], x0["k_w_img"],
+                     x0["rope_cos"], x0["rope_sin"], q16, k16, p_shard, stream=stream)
+
+    def attn_only(i):
+        ctx.run_on_handles(q16, k16, sets[i % n_sets]["v"][:, :, hsl], local, p_shard, stream=stream)
+
+    ms_attn = timed(attn_only)
+    status = ctx.last_status()
+    t = torch.tensor([ms_plain, ms_peer, ms_nccl, ms_attn, ms_1, float(not same_peer), float(not same_nccl), float(status)],
+                     dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_plain, ms_peer, ms_nccl, ms_attn, ms_1, bad_peer, bad_nccl, bad_status = t.tolist()
+    pg.close()
+    if bad_peer or bad_nccl or bad_status:
+        raise SystemExit(f"strong-scaling check failed: peer gather mismatch={bool(bad_peer)} nccl gather "
+                         f"mismatch={bool(bad_nccl)} status={int(bad_status)}")
+    biggest = max(s.count for s in shards)
+    attn_tflops = w.flops * biggest / w.heads / (ms_attn * 1e-3) / 1e12
+    best = min(ms_peer, ms_nccl)
+    return {
+        "workload": w.name, "partition": "heads of the one image split contiguously over the GPUs",
+        "heads_per_gpu": [s.count for s in shards], "ctas_per_gpu": biggest * ((w.tokens + 255) // 256),
+        "ms_per_step_1gpu": ms_1,
+        "ms_per_step": {"no_gather": ms_plain, "gather_by_epilogue_peer_stores": ms_peer, "gather_by_nccl_all_gather": ms_nccl},
+        "value": w.flops / (best * 1e-3) / 1e12, "unit": "TFLOP/s (whole call, gather included)",
+        "speedup_vs_1gpu": {"no_gather": ms_1 / ms_plain, "gather_by_epilogue_peer_stores": ms_1 / ms_peer,
+                            "gather_by_nccl_all_gather": ms_1 / ms_nccl},
+        "gather_share_of_step": {"epilogue_peer_stores": max(0.0, 1.0 - ms_plain / ms_peer),
+                                 "nccl_all_gather": max(0.0, 1.0 - ms_plain / ms_nccl)},
+        "gather_bytes_received_per_gpu": 2 * w.tokens * 128 * (w.heads - hs.count),
+        "attention": {"ms_per_launch": ms_attn, "achieved": attn_tflops, "unit": "TFLOP/s",
+                      "frac": attn_tflops / peaks["bf16_tflops"],
+                      "note": "one partial wave: CTAs per GPU against 148 SMs bounds this"},
+        "byte_check": "gathered O of every rank == the 1-GPU run of the whole call on that rank, byte for byte "
+                      "(both gather forms)",
+        "l2": f"inputs rotate over {n_sets} buffer sets ({n_sets * shard_bytes / 1e6:.0f} MB of shard operands)",
+    }
 
 
 def main():
@@ -445,6 +622,11 @@ def main():
     barrier()
     clocks = sampler.stop()
 
+    # ---- the metric call split by heads over the ranks (strong scaling), N > 1 only
+    strong = None
+    if world > 1 and not by_heads:
+        strong = strong_scaling_record(ctx, rank, world, min(args.steps, 50), args.warmup, stream, barrier, measured_peaks())
+
     # ---- max over ranks
     times = torch.tensor([ms_total, ms_prologue, ms_attention, t_e2e * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
@@ -469,8 +651,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong" if by_heads else "weak", "vs_baseline": None, "dtype": "f16 (f32 accumulate)",
             "data": "synthetic",
-            "config": {
-                "workload": w.name, "batch_per_gpu": w.batch, "heads": w.heads, "tokens": w.tokens, "head_dim": 128,
+            "config": workload_config(w, w.batch) | {
                 "flops_per_step_per_gpu": flops_rank, "step": "qk_norm_rope prologue + attention (joint call)",
                 "sharding": ("heads split over GPUs" + (", NCCL all-gather of O inside the step" if args.allgather
                              else ", no collective")) if by_heads else "one image (seed) per GPU, no collective",
@@ -483,9 +664,9 @@ def main():
                 "frac_of_sustained": attn_tflops / peaks["bf16_tflops_sustained"],
                 "frac_of_nominal_fp16": attn_tflops / NOMINAL_FP16_TFLOPS,
                 "ms_per_launch": ms_attention,
-                # dram__bytes_read.sum + dram__bytes_write.sum of one launch (one ncu capture of this
-                # workload, profiles/attn_fwd_kernel_klein_1024.md); other workloads were not captured.
-                "traffic": 90.5e6 if (w.name == "klein_1024" and not by_heads) else None, "traffic_unit": "B per launch",
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu counters kept
+                # beside the profile summaries; null for workloads that were not captured.
+                "traffic": None if by_heads else captured_traffic("attn_fwd_kernel", w.name), "traffic_unit": "B per launch",
                 "algorithmic_bytes": 4 * w.batch * w.tokens * hs.count * 128 * 2,
             },
             "prologue": {"kernel": "qk_norm_rope_kernel", "bound": "hbm", "achieved": prologue_gbs,
@@ -509,6 +690,8 @@ def main():
         if wide is not None:
             wide["frac"] = wide["achieved"] / peaks["bf16_tflops"]
             line["wide_attention"] = wide
+        if strong is not None:
+            line["strong"] = strong
         if world == 1 and not args.no_cpu_baseline:
             import oracle
 

@@ -264,6 +264,34 @@ ZDRAW_CUDA_API int zdraw_cuda_zimage_rope_table_device(void *ctx, void *stream, 
                                                        const size_t lens[3], float theta);
 
 /*
+ * Head sharding over the GPUs of a node (every (image, head) is an independent attention
+ * problem: the reference itself runs attention per image and per head-grid row,
+ * src/klein/zflux2_resident.zig:1728-1744, 1798-1833; src/metal/metal_api.m:6717). A GPU that
+ * computes heads [first_head, first_head + p->heads) of a call can hand its finished O tiles
+ * straight to every GPU of the group: while gather targets are set on a context, every
+ * zdraw_cuda_attention / zdraw_cuda_joint_attention call on it with f16 output also writes each
+ * O tile into each target, a head-major f16 buffer [image][total_heads][token][128], at head
+ * first_head + (head index within the call), with plain global stores from the attention
+ * epilogue (no multicast, no tensor map over the target, nothing is read from it). The targets
+ * may be peer mappings of other GPUs' memory; the stores are complete when the stream reaches
+ * the end of the call, and telling the other GPUs so (an event, a collective, a flag) is the
+ * caller's part. n_targets = 0 switches it off. No counterpart in the reference (single GPU).
+ */
+ZDRAW_CUDA_API int zdraw_cuda_attn_set_gather(void *ctx, uint32_t n_targets, void *const *targets,
+                                              uint32_t total_heads, uint32_t first_head);
+
+/*
+ * Device memory that the other processes of the node can map (one process per GPU): a plain
+ * cudaMalloc whose CUDA IPC handle (64 bytes) is written to handle64; the other processes pass
+ * the handle to zdraw_cuda_shared_open and get a peer mapping to use as a gather target. Free /
+ * close with the matching call. No counterpart in the reference.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_shared_alloc(void *ctx, size_t bytes, void **dev_ptr, void *handle64);
+ZDRAW_CUDA_API int zdraw_cuda_shared_free(void *ctx, void *dev_ptr);
+ZDRAW_CUDA_API int zdraw_cuda_shared_open(void *ctx, const void *handle64, void **dev_ptr);
+ZDRAW_CUDA_API int zdraw_cuda_shared_close(void *ctx, void *dev_ptr);
+
+/*
  * Reads (and clears) the device status word. 0 = every kernel ran to the end.
  * Non-zero = a kernel gave up a bounded wait and returned early; the output of
  * that call is invalid. Synchronises `stream`. Plays the part of the bridge's

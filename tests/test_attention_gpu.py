@@ -304,3 +304,35 @@ def test_pipeline_trace_facility(ctx):
     mma_steps = t[0, :6, 0]
     assert (mma_steps > 0).all() and (np.diff(mma_steps) > 0).all(), "MMA step stamps must increase"
     assert not t[0, 6:].any(), "only six K/V steps were run"
+
+
+def test_gather_targets_receive_every_tile(ctx):
+    """Head sharding: while gather targets are set, the attention epilogue also writes its O tiles into
+    each target at (first_head + head); other heads of the targets stay untouched; the regular output is
+    unchanged. Two local buffers stand in for the ranks' buffers (one of them would be a peer mapping)."""
+    w = workloads.Workload("gather_case", "klein", 2, 3, 512, 9, 9, seed=31)  # S = 593: ragged last tile
+    x = workloads.make_inputs(w, "cuda")
+    p = workloads.params(w, out_layout=_lib.LAYOUT_HEAD_MAJOR)
+    want = torch.empty((w.batch, w.heads, w.tokens, 128), dtype=torch.float16, device="cuda")
+    ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                        x["rope_cos"], x["rope_sin"], want, p)
+    total, first = 5, 1
+    targets = [torch.empty((w.batch, total, w.tokens, 128), dtype=torch.float16, device="cuda") for _ in range(2)]
+    for t in targets:
+        t.view(torch.uint8).fill_(0xFF)
+    got = torch.empty_like(want)
+    ctx.set_gather([t.data_ptr() for t in targets], total, first)
+    try:
+        ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                            x["rope_cos"], x["rope_sin"], got, p)
+        with pytest.raises(mattn.InvalidShape):  # heads [4, 7) do not fit 5
+            ctx.set_gather([t.data_ptr() for t in targets], total, 4)
+            ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                                x["rope_cos"], x["rope_sin"], got, p)
+    finally:
+        ctx.set_gather(None)
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    for t in targets:
+        assert torch.equal(t[:, first:first + w.heads].view(torch.int16), want.view(torch.int16))
+        assert bool((t[:, :first].view(torch.uint8) == 0xFF).all()) and bool((t[:, first + w.heads:].view(torch.uint8) == 0xFF).all())

@@ -276,6 +276,18 @@ int run_attention(Ctx* c, cudaStream_t stream, const void* q16, const void* k16,
   a.o_head_major = o_hm ? 1 : 0;
   a.o_tma = p->out_dtype == ZDRAW_DTYPE_F16 ? 1 : 0;
   if (a.o_tma && (rc = make_tmap(c, &tm_o, o, o_hm, s, s.ld_o)) != 0) return rc;
+  a.n_gather = 0;
+  a.gather_heads = a.gather_head0 = 0;
+  if (c->n_gather > 0) {
+    if (!a.o_tma) return fail(c, ZDRAW_CUDA_DECLINED, "gather targets need f16 output");
+    if (c->gather_head0 + s.heads > c->gather_heads)
+      return fail(c, ZDRAW_CUDA_E_ARG, "gather: heads [%d, %d) do not fit %d heads", c->gather_head0,
+                  c->gather_head0 + s.heads, c->gather_heads);
+    a.n_gather = c->n_gather;
+    a.gather_heads = c->gather_heads;
+    a.gather_head0 = c->gather_head0;
+    for (int i = 0; i < c->n_gather; ++i) a.gather[i] = c->gather[i];
+  }
   a.status = c->d_status;
   a.trace = c->d_trace;
   ZD_CUDA(c, zdraw::launch_attn_fwd(stream, tm_q, tm_k, tm_v, tm_o, a));
@@ -566,6 +578,71 @@ int zdraw_cuda_attention_host(void* ctx, const void* q, const void* k, const voi
   uint32_t status = 0;
   ZD_CUDA(c, cudaMemcpy(&status, c->d_status, sizeof(status), cudaMemcpyDeviceToHost));
   if (status != 0) return fail(c, ZDRAW_CUDA_E_DEVICE, "kernel gave up a bounded wait (status 0x%x)", status);
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_attn_set_gather(void* ctx, uint32_t n_targets, void* const* targets, uint32_t total_heads,
+                               uint32_t first_head) {
+  Ctx* c = as_ctx(ctx);
+  if (!c) return ZDRAW_CUDA_E_ARG;
+  if (n_targets == 0) {
+    c->n_gather = 0;
+    return ZDRAW_CUDA_OK;
+  }
+  if (n_targets > static_cast<uint32_t>(zdraw::kMaxGather) || !targets || total_heads == 0 || first_head >= total_heads ||
+      total_heads > 65535u)
+    return fail(c, ZDRAW_CUDA_E_ARG, "gather: 1..%d targets, first_head < total_heads", zdraw::kMaxGather);
+  for (uint32_t i = 0; i < n_targets; ++i)
+    if (!targets[i] || !aligned16(targets[i])) return fail(c, ZDRAW_CUDA_E_ARG, "gather target %u is null or misaligned", i);
+  c->n_gather = static_cast<int>(n_targets);
+  c->gather_heads = static_cast<int>(total_heads);
+  c->gather_head0 = static_cast<int>(first_head);
+  for (uint32_t i = 0; i < n_targets; ++i) c->gather[i] = targets[i];
+  return ZDRAW_CUDA_OK;
+}
+
+// Device memory that other processes of the node can map: plain cudaMalloc (so that an IPC handle
+// names exactly this allocation), exported and opened with the CUDA IPC calls.
+int zdraw_cuda_shared_alloc(void* ctx, size_t bytes, void** dev_ptr, void* handle64) {
+  Ctx* c = as_ctx(ctx);
+  if (!c || !dev_ptr || !handle64 || bytes == 0) return ZDRAW_CUDA_E_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  ZD_CUDA(c, cudaMalloc(dev_ptr, bytes));
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, *dev_ptr);
+  if (e != cudaSuccess) {
+    cudaFree(*dev_ptr);
+    *dev_ptr = nullptr;
+    return fail(c, ZDRAW_CUDA_E_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  }
+  memcpy(handle64, &h, sizeof(h));
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_shared_free(void* ctx, void* dev_ptr) {
+  Ctx* c = as_ctx(ctx);
+  if (!c || !dev_ptr) return ZDRAW_CUDA_E_ARG;
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  ZD_CUDA(c, cudaFree(dev_ptr));
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_shared_open(void* ctx, const void* handle64, void** dev_ptr) {
+  Ctx* c = as_ctx(ctx);
+  if (!c || !dev_ptr || !handle64) return ZDRAW_CUDA_E_ARG;
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  ZD_CUDA(c, cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_shared_close(void* ctx, void* dev_ptr) {
+  Ctx* c = as_ctx(ctx);
+  if (!c || !dev_ptr) return ZDRAW_CUDA_E_ARG;
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  ZD_CUDA(c, cudaIpcCloseMemHandle(dev_ptr));
   return ZDRAW_CUDA_OK;
 }
 

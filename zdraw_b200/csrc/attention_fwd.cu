@@ -775,8 +775,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tma_store_4d(&tm_o, src, 0, c1(a.o_head_major, tok0), c2(a.o_head_major, tok0), img);
           tma_store_4d(&tm_o, src + kHalfBytes, 64, c1(a.o_head_major, tok0), c2(a.o_head_major, tok0), img);
           bulk_commit_group();
-          bulk_wait_group_read<0>();  // the block must outlive the reads of the copy engine
         }
+        if (a.n_gather > 0) {
+          // The same tile to every gather target: the warpgroup copies the staged block row by
+          // row, a 256-byte row per 16 lanes, so that every store instruction covers whole lines
+          // (the targets may be other GPUs' memory; partial lines are what NVLink likes least).
+          const int tok0 = (q_tile0 + t) * kBM;
+          const int rows_valid = min(kBM, a.tokens - tok0);
+          const int piece = static_cast<int>(threadIdx.x) & 15;         // 16-byte piece of the row
+          const int row_in_pass = (static_cast<int>(threadIdx.x) & 127) >> 4;  // 8 rows per pass
+          const size_t tile_off = ((static_cast<size_t>(img) * a.gather_heads + a.gather_head0 + head) * a.tokens + tok0) * kBM;
+          for (int g = 0; g < a.n_gather; ++g) {
+            __half* dst = static_cast<__half*>(a.gather[g]) + tile_off;
+#pragma unroll 4
+            for (int r0 = 0; r0 < kBM; r0 += 8) {
+              const int r = r0 + row_in_pass;
+              if (r < rows_valid) {
+                const uint4 w = *reinterpret_cast<const uint4*>(qblk + (piece >> 3) * kHalfBytes + r * 128 +
+                                                                (((piece & 7) ^ (r & 7)) << 4));
+                *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * kBM + piece * 8) = w;
+              }
+            }
+          }
+        }
+        if (row == 0) bulk_wait_group_read<0>();  // the block must outlive the reads of the copy engine
       } else {
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {

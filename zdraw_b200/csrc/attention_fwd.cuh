@@ -9,6 +9,8 @@
 
 namespace zdraw {
 
+constexpr int kMaxGather = 8;
+
 // Arguments of the tcgen05 kernel besides its three tensor maps. q, k and v are
 // reached only through the tensor maps: 4-D, fp16, 128-byte swizzle, box 64 x 128 rows.
 // Dimension order is (d, token, head, image) for a head-major tensor and
@@ -36,6 +38,12 @@ struct AttnArgs {
   // stores 128 x 64 blocks as tiles. 0: rows are stored from registers. o_head_major names the
   // order of the map's middle coordinates.
   int o_tma, o_head_major;
+  // Gather targets (head sharding over GPUs): when n_gather > 0 every finished f16 O tile is also
+  // written, with plain 16-byte global stores, into each of these head-major buffers
+  // [image][gather_heads][token][128] at head gather_head0 + (this launch's head index). The
+  // buffers may live in other GPUs' memory (peer mappings); they are never read here.
+  int n_gather, gather_heads, gather_head0;
+  void* gather[kMaxGather];
   uint32_t* status;  // device status word
   unsigned long long* trace;  // nullptr, or attn_fwd_trace_words() words for pipeline time stamps (debugging)
 };

@@ -235,6 +235,8 @@ int zdraw_cuda_joint_attention_static(void* stream, const void* q, const void* k
   a.o_batch_stride = o_hm ? static_cast<long long>(heads) * tokens * kHeadDim : static_cast<long long>(tokens) * ld_o;
   a.o_tma = 0;  // rows are stored from registers; the fourth map is not read
   a.o_head_major = o_hm ? 1 : 0;
+  a.n_gather = 0;
+  a.gather_heads = a.gather_head0 = 0;
   a.status = st->status;
   a.trace = nullptr;
   if (zdraw::launch_attn_fwd(s, tm_q, tm_k, tm_v, tm_q, a) != cudaSuccess) return fail(ZDRAW_CUDA_E_CUDA, "attention launch failed");

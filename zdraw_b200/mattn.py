@@ -132,6 +132,32 @@ class Context:
         self._check(self._lib.zdraw_cuda_last_status(self._h, self._stream_ptr(stream), C.byref(st)))
         return int(st.value)
 
+    # ------------------------------------------------------------------ head sharding over GPUs
+    def set_gather(self, targets, total_heads: int = 0, first_head: int = 0) -> None:
+        """While set, every f16 attention call on this context also writes its O tiles into each of
+        ``targets`` (device pointers as ints: head-major ``[image][total_heads][token][128]`` f16
+        buffers, possibly peer mappings) at head ``first_head + local head``. ``None``/empty = off."""
+        targets = list(targets or [])
+        arr = (C.c_void_p * max(len(targets), 1))(*[C.c_void_p(int(t)) for t in targets])
+        self._check(self._lib.zdraw_cuda_attn_set_gather(self._h, len(targets), arr, int(total_heads), int(first_head)))
+
+    def shared_alloc(self, nbytes: int):
+        """Device memory the node's other processes can map: (device pointer, 64-byte IPC handle)."""
+        ptr, handle = C.c_void_p(), C.create_string_buffer(64)
+        self._check(self._lib.zdraw_cuda_shared_alloc(self._h, int(nbytes), C.byref(ptr), handle))
+        return int(ptr.value), bytes(handle.raw)
+
+    def shared_open(self, handle: bytes) -> int:
+        ptr = C.c_void_p()
+        self._check(self._lib.zdraw_cuda_shared_open(self._h, C.create_string_buffer(handle, 64), C.byref(ptr)))
+        return int(ptr.value)
+
+    def shared_close(self, ptr: int) -> None:
+        self._check(self._lib.zdraw_cuda_shared_close(self._h, C.c_void_p(ptr)))
+
+    def shared_free(self, ptr: int) -> None:
+        self._check(self._lib.zdraw_cuda_shared_free(self._h, C.c_void_p(ptr)))
+
     def reserve(self, params: AttnParams) -> None:
         self._check(self._lib.zdraw_cuda_attn_reserve(self._h, C.byref(params)))
 

@@ -8,11 +8,14 @@ with no exchange step:
 * ``heads``   – a contiguous range of heads per rank: pointer offset ``h0 * 128`` with the full
   token stride ``ld = H * 128`` (a column slice of the token-major tensors, no repacking).
 
-The only collective is the optional all-gather of the head shards' outputs when a whole block is
-timed: every rank contributes its heads in head-major form ``[heads_r, tokens, 128]`` and the
-gathered buffer is head-major ``[H, tokens, 128]`` (rank order == head order).
+The only exchange is the optional gather of the head shards' outputs when a whole block is
+timed: the gathered buffer is head-major ``[H, tokens, 128]`` (rank order == head order). Two
+forms: ``all_gather_heads`` (one collective after the kernel; NCCL on GPUs, gloo on CPU) and
+``PeerGather`` (the attention epilogue writes each finished tile into every rank's buffer with
+plain stores over NVLink, so the transfer is part of the kernel instead of a step after it).
 
-This module is pure host logic (no CUDA): ``tests/test_shard_gloo.py`` runs it on CPU ranks.
+``split`` / ``all_shards`` / ``all_gather_heads`` are pure host logic: ``tests/test_shard_gloo.py``
+runs them on CPU ranks.
 """
 from __future__ import annotations
 
@@ -76,3 +79,64 @@ def all_gather_heads(local_hm, heads: int, rank: int, world: int, group=None):
         return gathered
     parts = [gathered[r * biggest: r * biggest + s.count] for r, s in enumerate(shards)]
     return torch.cat(parts, dim=0)
+
+
+class _DevicePointer:
+    """A raw device allocation seen as a CUDA array (for ``torch.as_tensor``)."""
+
+    def __init__(self, ptr: int, shape, typestr: str = "<f2"):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
+class PeerGather:
+    """Gathered O buffers of one head-sharded call, one per rank, each mapped into every rank.
+
+    Every rank allocates ``[images, heads, tokens, 128]`` f16 with ``Context.shared_alloc`` (plain
+    ``cudaMalloc`` + CUDA IPC handle), the handles go round with ``all_gather_object`` and every rank
+    opens the others' buffers. ``targets`` is then the list of ``world`` device pointers (own buffer
+    first-class, peers as mappings) for ``Context.set_gather``; ``local`` is this rank's buffer as a
+    torch tensor. The stores of a step are complete on a rank when its stream has passed the call;
+    ``fence`` makes every rank wait until all ranks have got there (a one-element all-reduce).
+    """
+
+    def __init__(self, ctx, images: int, heads: int, tokens: int, rank: int, world: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
+        self.shape = (images, heads, tokens, 128)
+        nbytes = images * heads * tokens * 128 * 2
+        self._own, handle = ctx.shared_alloc(nbytes)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle, group=group)
+        self._opened = []
+        self.targets = []
+        for r in range(world):
+            if r == rank:
+                self.targets.append(self._own)
+            else:
+                p = ctx.shared_open(handles[r])
+                self._opened.append(p)
+                self.targets.append(p)
+        self.local = torch.as_tensor(_DevicePointer(self._own, self.shape), device=f"cuda:{ctx.device}")
+        self._token = torch.zeros(1, dtype=torch.int32, device=f"cuda:{ctx.device}")
+
+    def fence(self):
+        import torch.distributed as dist
+
+        dist.all_reduce(self._token, group=self.group)
+
+    def close(self):
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)  # nobody still writes into a buffer that is about to go
+        for p in self._opened:
+            self.ctx.shared_close(p)
+        self._opened = []
+        self.local = None
+        dist.barrier(group=self.group)
+        if self._own:
+            self.ctx.shared_free(self._own)
+            self._own = 0
