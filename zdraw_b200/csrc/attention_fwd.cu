@@ -9,7 +9,8 @@
 //               128B-swizzled shared-memory slots, a slot holding V of one K/V tile and K of
 //               the next (cp.async.bulk.tensor, no multicast)
 //   warp 1      MMA issuer: tcgen05.mma, S = Q K^T (both operands in shared memory)
-//               and O += P V (P read from tensor memory), accumulators in TMEM
+//               and O += P V (P read from tensor memory), accumulators in TMEM; barrier probes
+//               travel with the MMA batches
 //   warps 4-7   softmax for query tile 0, one thread per query row
 //   warps 8-11  softmax for query tile 1
 // (warps 2-3 idle; the first warpgroup gives most of its registers to the softmax
@@ -24,7 +25,16 @@
 // (steel_attention.h:166, mfa-fwd-d128.metal:999, mattn_block_shader.zig:39):
 // p = exp2(s*scale*log2e - m*scale*log2e), fp32 running max m and sum l.
 // The accumulator rescale is lazy: O and l are rescaled only when a row's max grew
-// by more than 2^8, a decision that depends on the data alone.
+// by more than 2^8, a decision that depends on the data alone. That also lets the first
+// exponentials of a step run against the previous steps' maximum while the new maximum is
+// still being reduced (the reduction is off the chain S -> P -> P V -> next S).
+//
+// P reaches the MMA warp in three pieces (keys [0,64), [64,96), [96,128)), so that O += P V
+// starts while the last keys are still being exponentiated. The MMA-issuing thread probes the
+// barrier of the next piece (or of the next K/V slot) inside the asm block that issues the
+// current batch of MMAs: a ready-barrier poll costs 100-170 clocks, which would otherwise be
+// tensor-pipe idle time after every batch (measured: five exposed polls per K/V step take the
+// issuing thread from 2048 to 2890 clocks per step, probes inside the batches to 2200).
 //
 // TMEM columns: [0,128) S/P tile 0, [128,256) S/P tile 1, [256,384) O tile 0,
 // [384,512) O tile 1. P (fp16) overwrites the first 64 columns of its S.
@@ -52,28 +62,16 @@ constexpr int kThreads = 384;
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 constexpr float kRescaleThreshold = 8.0f;                       // log2 units
 constexpr int kTraceIters = 40, kTraceEvents = 8;
-#ifndef ZD_EMU
-#define ZD_EMU 0
-#endif
-#ifndef ZD_FOLDMAX
-#define ZD_FOLDMAX 1
-#endif
-#ifndef ZD_HIDEPOLL
-#define ZD_HIDEPOLL 1
-#endif
-#ifndef ZD_PIECES
-#define ZD_PIECES 3
-#endif
 // P of a K/V step reaches the MMA warp in pieces, so that O += P V starts on the first keys while
 // the last ones are still being exponentiated. Piece ends in units of 16 keys (one MMA K-step):
 // 2 pieces {4, 8}, 3 pieces {4, 6, 8}, 4 pieces {2, 4, 6, 8}.
-constexpr int kPieces = ZD_PIECES;
+constexpr int kPieces = 3;
 static_assert(kPieces >= 2 && kPieces <= 4, "piece count");
 __host__ __device__ constexpr int piece_end(int i) {
   return kPieces == 2 ? 4 * (i + 1) : (kPieces == 3 ? (i == 0 ? 4 : (i == 1 ? 6 : 8)) : 2 * (i + 1));
 }
 __host__ __device__ constexpr int piece_begin(int i) { return i == 0 ? 0 : piece_end(i - 1); }
-constexpr int kEmuPairsOf4 = ZD_EMU;  // of every 4 score pairs, how many take the FMA-pipe exp2 (0..4)
+constexpr int kEmuPairsOf4 = 0;  // of every 4 score pairs, how many take the FMA-pipe exp2 (0..4)
 // Register budgets after setmaxnreg. The CTA is launched with 168 registers per thread
 // (3 warpgroups x 168 = 504 per lane triple); what the control warpgroup gives up is all the
 // softmax warpgroups can take, so kRegsControl + 2 * kRegsSoftmax must not exceed 504
@@ -277,19 +275,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           stamp(3, i, 1);
           const uint32_t dst = base + kOffKV + slot * 2 * kTileBytes;
           const bool has_v = i >= 1, has_k = i < n_act;
-#ifdef ZD_ABLATE_HALFLOAD  // timing experiment only (wrong results): half of the K/V bytes are fetched
-          mbar_arrive_expect_tx(bar(kBarKVFull + slot), (has_v ? kHalfBytes : 0) + (has_k ? kHalfBytes : 0));
-          if (has_v) {
-            const int row = (tile_entry(i - 1) & kTileIndexMask) * kBN;
-            const int hm = a.v_head_major;
-            tma_load_4d(dst, &tm_v, bar(kBarKVFull + slot), 0, c1(hm, row), c2(hm, row), img);
-          }
-          if (has_k) {
-            const int row = (tile_entry(i) & kTileIndexMask) * kBN;
-            const int hm = a.k_head_major;
-            tma_load_4d(dst + kTileBytes, &tm_k, bar(kBarKVFull + slot), 0, c1(hm, row), c2(hm, row), img);
-          }
-#else
           mbar_arrive_expect_tx(bar(kBarKVFull + slot), (has_v ? kTileBytes : 0) + (has_k ? kTileBytes : 0));
           if (has_v) {
             const int row = (tile_entry(i - 1) & kTileIndexMask) * kBN;
@@ -303,7 +288,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tma_load_4d(dst + kTileBytes, &tm_k, bar(kBarKVFull + slot), 0, c1(hm, row), c2(hm, row), img);
             tma_load_4d(dst + kTileBytes + kHalfBytes, &tm_k, bar(kBarKVFull + slot), 64, c1(hm, row), c2(hm, row), img);
           }
-#endif
         }
         if (!ok) {
           // Let copies that are still in flight land before the CTA's shared memory goes away.
@@ -356,7 +340,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_commit(bar(kBarSFull + 1));
           umma_commit(bar(kBarKVEmpty + 0));
         }
-#if ZD_HIDEPOLL
         // Steps with a successor: every barrier the next batch of MMAs depends on is probed
         // ahead of the current batch (inside its asm block), so a probe that finds the phase
         // complete costs the tensor pipe nothing; one that does not falls back to a wait.
@@ -427,11 +410,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // The last step (or the only one) takes the plain path below; what was probed for it counts.
         for (int jj = jj0; jj < n_act && ok; ++jj) {
           const uint32_t pair = static_cast<uint32_t>(jj) + 1u;
-#else
-        for (int jj = 0; jj < n_act && ok; ++jj) {
-          // Pair jj + 1: V of this step's tile and K of the next step's.
-          const uint32_t pair = static_cast<uint32_t>(jj) + 1u;
-#endif
           const uint32_t slot = pair % kPairStages;
           stamp(4, jj, 0);
           ok = wait_bar(bar(kBarKVFull + slot), (pair / kPairStages) & 1u, abort_flag, a.status, kStMma);
@@ -538,7 +516,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int i = 0; i < 128; ++i) s[i] = (i < tail) ? s[i] : -INFINITY;
       }
 
-#if ZD_FOLDMAX
       // The row maximum is taken off the chain S -> P: the exponentials of the first 64 keys are
       // computed against the running maximum m of the steps before, while the maximum of all 128
       // new scores is reduced beside them (the exponentials keep the MUFU busy, the reduction
@@ -640,93 +617,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_st_x16(t_s + 48u, pk1);
       publish(3);
       if (tr) stamp(1 + t, jj, 5);
-#else
-      float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
-      float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
-#pragma unroll
-      for (int i = 12; i < 124; i += 8) {
-        mx0 = max3(mx0, s[i], s[i + 1]);
-        mx1 = max3(mx1, s[i + 2], s[i + 3]);
-        mx2 = max3(mx2, s[i + 4], s[i + 5]);
-        mx3 = max3(mx3, s[i + 6], s[i + 7]);
-      }
-      mx0 = max3(mx0, s[124], s[125]);
-      mx1 = max3(mx1, s[126], s[127]);
-      const float m_new = max3(m, fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-
-      if (jj == 0) {
-        m = m_new;
-      } else {
-        // PV of the previous step has completed: the commit that released S covers it.
-        const bool need = (m_new - m) * c > kRescaleThreshold;
-        if (__any_sync(0xffffffffu, need)) {
-          float alpha = 1.0f;
-          if (need) {
-            alpha = ex2_approx((m - m_new) * c);
-            m = m_new;
-          }
-          l *= alpha;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint32_t o[32];
-            tmem_ld_x32(t_o + 32u * ch, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_x32(t_o + 32u * ch, o);
-          }
-          tmem_wait_st();
-        }
-      }
-
-      if (tr) stamp(1 + t, jj, 3);
-      const float mc = (m == -INFINITY) ? 0.0f : m * c;
-      // p = exp2(s*c - m*c) on pairs. Of every four pairs, kEmuPairsOf4 are evaluated on the FMA
-      // pipe (round-to-nearest split x = n + r, |r| <= 0.5, cubic for 2^r, n added to the
-      // exponent), the rest with MUFU ex2 (16/clk/SM). Measured on B200 the MUFU-only setting
-      // (0) is the fastest in wall time, so it is the default. -inf scores (masked or ragged
-      // tiles) are safe on both paths: MUFU gives 0, the FMA-pipe path clamps its argument and
-      // gives 2^-126, which rounds to 0 in P.
-      const uint64_t c2 = f2_pack(c, c);
-      const uint64_t nmc2 = f2_pack(-mc, -mc);
-      uint64_t acc0 = 0ull, acc1 = 0ull;  // packed partial row sums (+0.0f, +0.0f)
-      {
-        constexpr int kEmu = kEmuPairsOf4;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int e = 32 * ch + 2 * i;
-            const uint64_t x2 = f2_fma(f2_pack(s[e], s[e + 1]), c2, nmc2);
-            uint64_t p2;
-            if ((i & 3) < kEmu) {
-              p2 = exp2_emulated_pair(x2);
-            } else {
-              float x0, x1;
-              f2_unpack(x2, x0, x1);
-              p2 = f2_pack(ex2_approx(x0), ex2_approx(x1));
-            }
-            if (i & 1) acc1 = f2_add(acc1, p2); else acc0 = f2_add(acc0, p2);
-            float p0, p1;
-            f2_unpack(p2, p0, p1);
-            pk[i] = pack_f16x2(p0, p1);
-          }
-          tmem_st_x16(t_s + 16u * ch, pk);
-          // Chunk ch holds MMA K-steps 2 ch and 2 ch + 1: a piece of P is handed to the MMA warp as
-          // soon as its last chunk has been stored.
-#pragma unroll
-          for (int i = 0; i < kPieces; ++i) {
-            if (piece_end(i) == 2 * (ch + 1)) {
-              tmem_wait_st();
-              tc_fence_before();
-              mbar_arrive(bar(kBarPFull + kPieces * t + i));
-            }
-          }
-          if (tr && (ch == 1 || ch == 3)) stamp(1 + t, jj, 4 + (ch >> 1));
-        }
-      }
-#endif
       {
         float a0, a1, b0, b1;
         f2_unpack(acc0, a0, a1);
