@@ -300,6 +300,18 @@ ZDRAW_CUDA_API int zdraw_cuda_shared_close(void *ctx, void *dev_ptr);
 ZDRAW_CUDA_API int zdraw_cuda_last_status(void *ctx, void *stream, uint32_t *device_status);
 
 /*
+ * Self-test of the failure path: runs one tiny kernel on `stream` whose bounded waits (the very
+ * routine every kernel of this library waits with) look for an mbarrier phase that nothing
+ * completes. After limit_ns (at most 100 ms) they give up, set bit 8 of the context's status word
+ * and the kernel ends normally - nothing traps, faults or spins without a limit. Until the word is
+ * read with zdraw_cuda_last_status, later kernels on the context return at once and the
+ * host-buffer calls answer ZDRAW_CUDA_E_DEVICE, exactly as after a real give-up. Follows the
+ * reference's counted-fallback convention (metal_api.m:350, 459, 6785): a route that did not run
+ * to the end is reported, never silently accepted.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_selftest_wait_timeout(void *ctx, void *stream, uint64_t limit_ns);
+
+/*
  * Projection GEMM for the steps either side of attention: C[m, n] = A[m, k] * W[n, k]^T with f16
  * A and W and f32 accumulation. Replaces zdraw_metal_run_gemm_enc as the DiT blocks use it for
  * the q/k/v and output projections (gemmRunF16A, src/klein/zflux2_resident.zig:924-990; call
@@ -364,6 +376,16 @@ ZDRAW_CUDA_API int zdraw_cuda_qkv_projection(void *ctx, void *stream, const void
  */
 ZDRAW_CUDA_API int zdraw_cuda_wide_attention(void *ctx, void *stream, const float *q, const float *k, const float *v,
                                              float *o, size_t tokens, size_t head_dim);
+
+/*
+ * Which way the last zdraw_cuda_wide_attention call on this context took its row maxima: 0 = from
+ * the e4m3 copies of Q and K (admitted only when the operands' norms bound the error of every
+ * estimated maximum below 2^6 in the exponentials), 1 = from the half operands (the reference's
+ * exact form). The choice is made on the device from the data alone, so repeats take the same
+ * route. Plays the part of the bridge's per-route counters (metal_api.m:350, 459). Synchronises
+ * `stream`.
+ */
+ZDRAW_CUDA_API int zdraw_cuda_wide_attention_route(void *ctx, void *stream, uint32_t *exact_row_max);
 
 /*
  * Debugging aid, the counterpart of ZDRAW_KLEIN_TRACE's per-stage GPU times

@@ -35,19 +35,24 @@ def test_small_shapes_match_cpu_attention(ctx, oracle, tokens, dim):
     want = oracle.sdpa(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), heads=1)
     err = np.abs(out.cpu().numpy() - want.reshape(tokens, dim))
     assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS
+    if dim >= 256:
+        assert ctx.wide_attention_route() == 0  # N(0,1) operands: the e4m3 estimate of the row maxima is provably close
 
 
-@pytest.mark.parametrize("gain", [3.0, 6.0])
-def test_peaked_rows_survive_the_estimated_row_maximum(ctx, oracle, gain):
-    """Scores with a standard deviation of 9 and 36 (row maxima near 30 and 120): the row maximum
-    that is subtracted comes from an 8-bit product and is only an estimate, which must not cost
-    accuracy or overflow the half exponentials."""
+@pytest.mark.parametrize("gain,route", [(1.0, 0), (1.25, 0), (3.0, 1), (6.0, 1), (10.0, 1)])
+def test_peaked_rows_survive_the_estimated_row_maximum(ctx, oracle, gain, route):
+    """Scores with a standard deviation of 1, 1.6, 9, 36 and 100 (row maxima near 4, 6, 30, 120 and 330): the row
+    maximum that is subtracted may come from an 8-bit product, but only while the operands' norms prove that
+    estimate close; beyond that the exact maximum of the half products is taken, as the reference does
+    (krow_softmax_h). Either way nothing overflows, nothing is clamped and accuracy holds. The tolerance is the
+    fp16 one times two: a peaked softmax amplifies the rounding of P."""
     tokens, dim = 1024, 512
     q, k, v = make(tokens, dim, 5)
     q, k = q * gain, k * gain
     out = torch.full((tokens, dim), float("nan"), device="cuda")
     ctx.wide_attention(q, k, v, out, mattn.Config(tokens, 1, 1, dim))
     torch.cuda.synchronize()
+    assert ctx.wide_attention_route() == route
     assert ctx.last_status() == 0
     got = out.cpu().numpy()
     assert np.isfinite(got).all()
@@ -79,6 +84,28 @@ def test_vae_mid_block_shape_sampled_rows_and_repeat(ctx, oracle):
         want = oracle.sdpa(qh, kh, vh, heads=1, rows=(r, r + 1)).reshape(tokens, dim)[r]
         err = np.abs(got[r] - want)
         assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS, f"row {r}: {err.max()}"
+
+
+def test_values_beyond_the_e4m3_range_and_colliding_keys(ctx, oracle):
+    """Entries above 448 (where e4m3 saturates) and a dominant key whose 8-bit image equals a runner-up's:
+    an estimate from the 8-bit copies could miss the true maximum by far more than the half range holds,
+    so these calls must take the exact route, and still match the oracle."""
+    tokens, dim = 512, 512
+    q, k, v = make(tokens, dim, 11, scale=0.05)
+    k[7] = 0.0
+    k[9] = 0.0
+    k[7, 0], k[9, 0] = 500.0, 470.0   # both saturate to 448 in e4m3; key 7 wins by 30 * q[:, 0] / sqrt(512)
+    q[:, 0] = 20.0
+    out = torch.full((tokens, dim), float("nan"), device="cuda")
+    ctx.wide_attention(q, k, v, out, mattn.Config(tokens, 1, 1, dim))
+    torch.cuda.synchronize()
+    assert ctx.wide_attention_route() == 1 and ctx.last_status() == 0
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    want = oracle.sdpa(q.half().float().cpu().numpy(), k.half().float().cpu().numpy(), v.cpu().numpy(), heads=1)
+    err = np.abs(got - want.reshape(tokens, dim))
+    assert err.max() <= 2e-2 and err.mean() <= 2e-3
+    assert np.allclose(got, v[7].half().float().cpu().numpy()[None, :], atol=2e-3)  # key 7 takes everything
 
 
 def test_constant_values_and_peaked_scores(ctx):

@@ -85,10 +85,12 @@ SYMBOLS = {
     "zdraw_cuda_shared_free": (C.c_int, [_VP, _VP]),
     "zdraw_cuda_shared_open": (C.c_int, [_VP, _VP, C.POINTER(C.c_void_p)]),
     "zdraw_cuda_shared_close": (C.c_int, [_VP, _VP]),
+    "zdraw_cuda_selftest_wait_timeout": (C.c_int, [_VP, _VP, C.c_uint64]),
     "zdraw_cuda_last_status": (C.c_int, [_VP, _VP, C.POINTER(C.c_uint32)]),
     "zdraw_cuda_linear": (C.c_int, [_VP] * 9 + [C.POINTER(LinearParams)]),
     "zdraw_cuda_qkv_projection": (C.c_int, [_VP] * 15 + [C.POINTER(LinearParams)]),
     "zdraw_cuda_wide_attention": (C.c_int, [_VP] * 6 + [C.c_size_t, C.c_size_t]),
+    "zdraw_cuda_wide_attention_route": (C.c_int, [_VP, _VP, C.POINTER(C.c_uint32)]),
     "zdraw_cuda_attn_set_trace": (C.c_int, [_VP, _VP, C.c_size_t]),
     "zdraw_cuda_last_error": (C.c_char_p, [_VP]),
 }

@@ -354,7 +354,7 @@ int zdraw_cuda_attn_destroy(void* ctx) {
   cudaDeviceSynchronize();
   Buf* bufs[] = {&c->q16, &c->k16, &c->v16, &c->tile_list, &c->st_q, &c->st_k, &c->st_v,
                  &c->st_o, &c->st_w, &c->st_cos, &c->st_sin, &c->st_mask,
-                 &c->wa_q16, &c->wa_k16, &c->wa_vt16, &c->wa_aux, &c->wa_p, &c->wa_q8, &c->wa_k8};
+                 &c->wa_q16, &c->wa_k16, &c->wa_vt16, &c->wa_aux, &c->wa_p, &c->wa_q8, &c->wa_k8, &c->wa_stats};
   for (Buf* b : bufs)
     if (b->p) cudaFree(b->p);
   if (c->d_status) cudaFree(c->d_status);
@@ -643,6 +643,16 @@ int zdraw_cuda_shared_close(void* ctx, void* dev_ptr) {
   if (!c || !dev_ptr) return ZDRAW_CUDA_E_ARG;
   ZD_CUDA(c, cudaSetDevice(c->device));
   ZD_CUDA(c, cudaIpcCloseMemHandle(dev_ptr));
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_selftest_wait_timeout(void* ctx, void* stream, uint64_t limit_ns) {
+  Ctx* c = as_ctx(ctx);
+  if (!c) return ZDRAW_CUDA_E_ARG;
+  if (limit_ns == 0 || limit_ns > 100ull * 1000ull * 1000ull)
+    return fail(c, ZDRAW_CUDA_E_ARG, "limit_ns must be in (0, 100 ms]");
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  ZD_CUDA(c, zdraw::launch_wait_timeout_probe(static_cast<cudaStream_t>(stream), c->d_status, limit_ns));
   return ZDRAW_CUDA_OK;
 }
 

@@ -47,6 +47,7 @@ struct Ctx {
   Buf st_q, st_k, st_v, st_o, st_w, st_cos, st_sin, st_mask;  // staging for the host-buffer path
   Buf wa_q16, wa_k16, wa_vt16, wa_aux, wa_p;  // wide-head attention: half operands, row statistics, exp(scores)
   Buf wa_q8, wa_k8;                            // e4m3 copies of Q and K for the row-max pass
+  Buf wa_stats;                                // operand statistics (2 + 2 words) and the row-max route word
   // Gather targets of the head-sharded call (zdraw_cuda_attn_set_gather); 0 = off.
   int n_gather = 0, gather_heads = 0, gather_head0 = 0;
   void* gather[8] = {};

@@ -21,6 +21,7 @@ struct PartSpec {
   const float* row_scale = nullptr;  // plain: optional factor per row
   unsigned int* row_key = nullptr;   // row max / exp: ordered keys of the row maxima
   float* row_sum = nullptr;          // exp: partial row sums
+  const float* max_shift = nullptr;  // exp: optional amount subtracted from every row maximum
   float exp_scale = 0.0f;
   uint32_t n_valid = 0;              // row max / exp: real columns (0 = all n); W then has n_valid rows
 };
@@ -31,7 +32,8 @@ struct PartSpec {
 // of halves; p->a_dtype / w_dtype still say f16 and strides count elements.
 int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec* parts, const float* rope_cos,
                const float* rope_sin, const zdraw_cuda_linear_params* p, bool operands_e4m3 = false,
-               uint32_t w_k_valid = 0) {  // columns of W that exist when fewer than k (A has all k)
+               uint32_t w_k_valid = 0,  // columns of W that exist when fewer than k (A has all k)
+               const unsigned int* gate = nullptr, int gate_run_if = 0) {  // device-side launch gate (linear.cuh)
   if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
   if (p->reserved != 0 || p->m == 0 || p->n == 0 || p->k == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero size or reserved != 0");
   if (p->c_dtype != ZDRAW_DTYPE_F16 && p->c_dtype != ZDRAW_DTYPE_F32) return fail(cx, ZDRAW_CUDA_E_ARG, "bad c_dtype");
@@ -65,6 +67,8 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
   la.fp8 = operands_e4m3 ? 1 : 0;
   la.n_parts = n_parts;
   la.status = cx->d_status;
+  la.gate = gate;
+  la.gate_run_if = gate_run_if;
   if (any_qk) {
     if (p->tokens == 0 || p->heads == 0 || p->m % p->tokens != 0 || p->n != p->heads * 128u || p->txt_tokens > p->tokens)
       return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs m = images * tokens and n = heads * 128");
@@ -94,6 +98,7 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
       lp.row_scale = parts[i].row_scale;
       lp.row_key = parts[i].row_key;
       lp.row_sum = parts[i].row_sum;
+      lp.max_shift = parts[i].max_shift;
       lp.exp_scale = parts[i].exp_scale;
       lp.n_valid = static_cast<int>(parts[i].n_valid ? parts[i].n_valid : p->n);
     }
@@ -176,24 +181,33 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   int rc;
   if ((rc = ensure(cx, cx->wa_q16, n * 2)) || (rc = ensure(cx, cx->wa_k16, n * 2)) || (rc = ensure(cx, cx->wa_vt16, n * 2)) ||
       (rc = ensure(cx, cx->wa_aux, aux_bytes)) || (rc = ensure(cx, cx->wa_p, tokens * n_pad * 2)) ||
-      (rc = ensure(cx, cx->wa_q8, n)) || (rc = ensure(cx, cx->wa_k8, n)))
+      (rc = ensure(cx, cx->wa_q8, n)) || (rc = ensure(cx, cx->wa_k8, n)) || (rc = ensure(cx, cx->wa_stats, 256)))
     return rc;
+  unsigned int* stats = static_cast<unsigned int*>(cx->wa_stats.p);  // [0,1] Q, [2,3] K, [4] route, [5] shift of the estimated maxima
+  const float exp_scale = 1.4426950408889634f / std::sqrt(static_cast<float>(head_dim));
   unsigned int* row_key = static_cast<unsigned int*>(cx->wa_aux.p);
   float* row_inv = reinterpret_cast<float*>(row_key + tokens);
   float* row_sum = row_inv + tokens;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // kf32_to_h x2, kvt_transpose_h (mvattn_owned.zig:322-330); Q and K also as e4m3 (see below)
-  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16_e4m3(st, q, cx->wa_q16.p, cx->wa_q8.p, static_cast<long long>(n)));
-  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16_e4m3(st, k, cx->wa_k16.p, cx->wa_k8.p, static_cast<long long>(n)));
+  ZD_CUDA(cx, cudaMemsetAsync(stats, 0, 32, st));
+  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16_e4m3(st, q, cx->wa_q16.p, cx->wa_q8.p, static_cast<long long>(tokens),
+                                                 static_cast<int>(head_dim), stats));
+  ZD_CUDA(cx, zdraw::launch_cast_f32_to_f16_e4m3(st, k, cx->wa_k16.p, cx->wa_k8.p, static_cast<long long>(tokens),
+                                                 static_cast<int>(head_dim), stats + 2));
+  ZD_CUDA(cx, zdraw::launch_wide_gate(st, stats, stats + 2, static_cast<int>(head_dim), exp_scale, stats + 4));
   ZD_CUDA(cx, zdraw::launch_transpose_cast(st, v, cx->wa_vt16.p, static_cast<int>(tokens), static_cast<int>(head_dim)));
   ZD_CUDA(cx, cudaMemsetAsync(row_key, 0, tokens * 4, st));  // key 0 lies below every float
   // The scores S = Q K^T (K is already [n][k]) are never stored. A first product keeps only each
   // row's maximum; a second one turns its accumulator into exp(scale (S - max)) in half and keeps
   // partial row sums: recomputing S (k = head_dim is short) costs less than writing and re-reading
   // tokens^2 f32 scores. Softmax does not change when another number than the exact maximum is
-  // subtracted, as long as nothing overflows, so the first product runs on e4m3 copies of Q and K
-  // at twice the rate: its maxima are a few percent of |S| off, and the exponentials are clamped
-  // to the half range.
+  // subtracted, as long as nothing overflows, so the first product may run on e4m3 copies of Q and
+  // K at twice the rate - when the operands' norms prove its maxima close enough (wide_gate_kernel:
+  // within 2^6 of the true ones in the exponentials). Both forms of that product are enqueued and
+  // the route word picks the one that does the work; the other launch leaves at once. (The
+  // reference takes the exact f32 maximum of half products, krow_softmax_h,
+  // src/metal/mvattn_owned.zig:95-128; the half-operand route is that.)
   zdraw_cuda_linear_params ps = {};
   ps.m = static_cast<uint32_t>(tokens);
   ps.n = static_cast<uint32_t>(n_pad);
@@ -203,11 +217,13 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   part_s.row_key = row_key;
   part_s.n_valid = static_cast<uint32_t>(tokens);
   part_s.w = cx->wa_k8.p;
-  if ((rc = run_linear(cx, stream, cx->wa_q8.p, 1, &part_s, nullptr, nullptr, &ps, true)) != 0) return rc;
+  if ((rc = run_linear(cx, stream, cx->wa_q8.p, 1, &part_s, nullptr, nullptr, &ps, true, 0, stats + 4, 0)) != 0) return rc;
   part_s.w = cx->wa_k16.p;
+  if ((rc = run_linear(cx, stream, cx->wa_q16.p, 1, &part_s, nullptr, nullptr, &ps, false, 0, stats + 4, 1)) != 0) return rc;
   part_s.epilogue = static_cast<uint32_t>(zdraw::kEpilogueExp);
   part_s.row_sum = row_sum;
-  part_s.exp_scale = 1.4426950408889634f / std::sqrt(static_cast<float>(head_dim));
+  part_s.exp_scale = exp_scale;
+  part_s.max_shift = reinterpret_cast<const float*>(stats + 5);
   if ((rc = run_linear(cx, stream, cx->wa_q16.p, 1, &part_s, nullptr, nullptr, &ps)) != 0) return rc;
   ZD_CUDA(cx, zdraw::launch_row_sum_inverse(st, row_sum, static_cast<int>(n_partial), static_cast<long long>(tokens), row_inv));
   // O[tokens, head_dim] = (P (V^T)^T) / row sum, f32 out
@@ -221,6 +237,18 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   PartSpec part_o = {cx->wa_vt16.p, o, 0, nullptr, nullptr};
   part_o.row_scale = row_inv;
   return run_linear(cx, stream, cx->wa_p.p, 1, &part_o, nullptr, nullptr, &po, false, static_cast<uint32_t>(tokens));
+}
+
+int zdraw_cuda_wide_attention_route(void* ctx, void* stream, uint32_t* exact_row_max) {
+  Ctx* cx = as_ctx(ctx);
+  if (!cx || !exact_row_max) return ZDRAW_CUDA_E_ARG;
+  *exact_row_max = 0;
+  if (!cx->wa_stats.p) return fail(cx, ZDRAW_CUDA_E_ARG, "no wide attention call has run on this context");
+  ZD_CUDA(cx, cudaSetDevice(cx->device));
+  ZD_CUDA(cx, cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  ZD_CUDA(cx, cudaMemcpy(exact_row_max, static_cast<const unsigned int*>(cx->wa_stats.p) + 4, sizeof(uint32_t),
+                         cudaMemcpyDeviceToHost));
+  return ZDRAW_CUDA_OK;
 }
 
 int zdraw_cuda_qkv_projection(void* ctx, void* stream, const void* x, const void* wq, const void* wk, const void* wv,

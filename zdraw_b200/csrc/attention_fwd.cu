@@ -101,6 +101,7 @@ constexpr int kSmemBytes = kOffFlags + 16 + 1024;  // + alignment slack
 constexpr uint32_t kStProducer = 1u << 0;
 constexpr uint32_t kStMma = 1u << 1;
 constexpr uint32_t kStSoftmax = 1u << 2;
+constexpr uint32_t kStWaitProbe = 1u << 8;  // the self-test kernel below
 
 // Tile-list entries: K/V tile index, plus a flag for tiles the key mask covers partly.
 constexpr int kTileMixedFlag = 0x40000000;
@@ -109,20 +110,7 @@ constexpr int kTileIndexMask = 0x3FFFFFFF;
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                          uint32_t* status, uint32_t code) {
   if (mbar_test_wait(bar, parity)) return true;  // the common case for the MMA-issuing thread
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        atomicOr(status, code);
-        return false;
-      }
-    }
-  }
+  return mbar_wait_bounded(bar, parity, abort_flag, status, code, kWaitLimitNs);
 }
 
 // 2^x for a packed pair on the FMA pipe. x is clamped to >= -126 so the exponent arithmetic
@@ -771,6 +759,27 @@ __global__ void attn_scalar_kernel(const ScalarArgs a) {
 
 
 // ---------------------------------------------------------------------------
+// Self-test of the bounded waits: two warps wait, with the kernels' own wait routine and a limit
+// given by the caller, for an mbarrier phase that nothing will ever complete. The first wait to
+// run out sets the CTA's abort flag and the status bit; the other one sees the flag (or runs out
+// itself) and returns too. The kernel then ends normally: no trap, no fault, no endless loop.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(64, 1) wait_timeout_probe_kernel(uint32_t* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long barrier_word;
+  __shared__ uint32_t abort_word;
+  const uint32_t bar = smem_u32(&barrier_word);
+  if (threadIdx.x == 0) {
+    abort_word = 0u;
+    mbar_init(bar, 1);  // one arrival expected; nobody arrives
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0)
+    (void)mbar_wait_bounded(bar, 0, &abort_word, status, kStWaitProbe, limit_ns);
+  __syncthreads();
+}
+
+// ---------------------------------------------------------------------------
 // Key-mask tile classification. One block per image, 128 threads = one tile's keys.
 // A tile is left out when every one of its keys is masked (-inf or beyond the
 // sequence), listed plain when all 128 keys exist and carry mask 0, else listed
@@ -839,6 +848,11 @@ cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const 
   cfg.numAttrs = 1;
   if (args.trace != nullptr) return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<true>, tm_q, tm_k, tm_v, tm_o, args);
   return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<false>, tm_q, tm_k, tm_v, tm_o, args);
+}
+
+cudaError_t launch_wait_timeout_probe(cudaStream_t stream, uint32_t* status, unsigned long long limit_ns) {
+  wait_timeout_probe_kernel<<<1, 64, 0, stream>>>(status, limit_ns);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args) {

@@ -67,6 +67,8 @@ cudaError_t attn_fwd_configure();  // raises the kernel's dynamic shared-memory 
 cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
                             const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args);
 cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args);
+// Self-test: one small CTA whose bounded waits run out after limit_ns and set bit 8 of *status.
+cudaError_t launch_wait_timeout_probe(cudaStream_t stream, uint32_t* status, unsigned long long limit_ns);
 // Classifies the K/V tiles of each image under `key_mask` and writes the tile lists
 // (1 + n_kv_tiles ints per image, `list_stride` ints apart).
 cudaError_t launch_mask_prepare(cudaStream_t stream, const float* key_mask, long long mask_batch_stride,

@@ -71,23 +71,11 @@ constexpr int kSmemBytes = kOffTab + 8 * kTabBytesPerWarp;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
 constexpr uint32_t kStLinear = 1u << 4;  // status bit: a bounded wait in this kernel gave up
+constexpr uint32_t kStExpClamp = 1u << 5;  // status bit: an exponential of the exp epilogue left the half range
 
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                          uint32_t* status) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1;
-        atomicOr(status, kStLinear);
-        return false;
-      }
-    }
-  }
+  return mbar_wait_bounded(bar, parity, abort_flag, status, kStLinear, kWaitLimitNs);
 }
 
 // Order-preserving map float -> unsigned (0 lies below every float), so that a row maximum can be
@@ -121,7 +109,7 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int tiles_n = (a.n + kTN - 1) / kTN;            // column blocks of one part (the last may be partial)
   const int tiles_m = (a.m + 2 * kTM - 1) / (2 * kTM);  // pair tiles: 256 rows
-  const int n_tiles = tiles_m * tiles_n * a.n_parts;
+  int n_tiles = tiles_m * tiles_n * a.n_parts;
   // A stage is a 128-byte slice of K per row; rows, columns and K beyond the matrices read as zeros.
   const int k_steps = a.fp8 ? (a.k + 2 * kTK - 1) / (2 * kTK) : (a.k + kTK - 1) / kTK;
   const int k_per_stage = a.fp8 ? 2 * kTK : kTK;
@@ -159,6 +147,8 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
   tc_fence_after();
   const uint32_t tmem_base = flags[1];
   grid_dependency_wait();
+  // A gated launch that is not the chosen one has no tiles (both CTAs of a pair see the same word).
+  if (a.gate != nullptr && ((*a.gate != 0u) != (a.gate_run_if != 0))) n_tiles = 0;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -300,9 +290,11 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
         const bool exp_mode = part.epilogue == kEpilogueExp;
         // plain: optional factor of this row; exp: x -> exp2(x * c + bias), bias = -max * c
         float mul = 1.0f, bias = 0.0f, psum = 0.0f;
+        bool clamped = false;
         if (exp_mode) {
           mul = part.exp_scale;
-          bias = live ? -key_float(part.row_key[m]) * part.exp_scale : 0.0f;
+          const float shift = part.max_shift ? *part.max_shift : 0.0f;
+          bias = live ? -(key_float(part.row_key[m]) - shift) * part.exp_scale : 0.0f;
         } else if (part.row_scale != nullptr && live) {
           mul = part.row_scale[m];
         }
@@ -336,11 +328,15 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
               const int n_live = part.n_valid - (col_base + 32 * pc);  // columns of this piece that exist
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
-                // (the subtracted maximum may be an estimate: keep the result in the half range)
-                float e0 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias)), kHalfMax);
-                float e1 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias)), kHalfMax);
+                // (the subtracted maximum may be an estimate, admitted only with a proven error bound:
+                // a result beyond the half range means that bound was broken, and is reported)
+                float e0 = ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias));
+                float e1 = ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias));
                 if (2 * i >= n_live) e0 = 0.0f;
                 if (2 * i + 1 >= n_live) e1 = 0.0f;
+                clamped = clamped || !(e0 <= kHalfMax) || !(e1 <= kHalfMax);
+                e0 = fminf(e0, kHalfMax);
+                e1 = fminf(e1, kHalfMax);
                 psum += e0 + e1;  // f32 sum of the unrounded values, as the reference's softmax takes it
                 const __half2 v = __floats2half2_rn(e0, e1);
                 h[i] = *reinterpret_cast<const uint32_t*>(&v);
@@ -362,6 +358,7 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
           }
         }
         if (exp_mode && live) part.row_sum[m * (2 * tiles_n) + 2 * tile_n + hh] = psum;
+        if (exp_mode && live && clamped) atomicOr(a.status, kStExpClamp);
       } else {
         // qk epilogue: the tile's 256 columns are two heads of this token's projection.
         const long long mm = live ? m : 0;

@@ -28,6 +28,7 @@ struct LinearPart {
   unsigned int* row_key;
   float* row_sum;
   float exp_scale;
+  const float* max_shift;  // exp: optional, one float: subtracted from every row maximum before use
   // row max / exp: columns at and beyond n_valid are padding of the last column block (W has no
   // such rows): they do not count for the maximum and are stored as zeros.
   int n_valid;
@@ -48,6 +49,11 @@ struct LinearArgs {
   const float *rope_cos, *rope_sin;  // [tokens][128]
   long long rope_batch_stride;
   uint32_t* status;
+  // Optional launch gate: when set, the kernel does its work only if (*gate != 0) == (gate_run_if != 0),
+  // read after the preceding kernel in the stream has finished; otherwise every CTA leaves at once.
+  // Lets the host enqueue two alternative launches and a device-side decision pick one.
+  const unsigned int* gate;
+  int gate_run_if;
 };
 
 struct LinearMaps {

@@ -73,6 +73,30 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Bounded wait for the phase `parity` of an mbarrier. Returns true when the phase has completed.
+// Gives up - sets *abort_flag (a flag of the CTA, which makes every other bounded wait of the CTA
+// return false at its next look) and ORs `code` into the device status word - once `limit_ns` of
+// wall time have passed, or returns false as soon as another wait of the CTA has given up. Nothing
+// traps and nothing spins without a limit: the kernel's roles leave their loops, and the host
+// reads the status word (zdraw_cuda_last_status; ZDRAW_CUDA_E_DEVICE from the host-buffer calls).
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t* status, uint32_t code, uint64_t limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        *abort_flag = 1;
+        atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- TMA
 // 4-D tiled load global -> shared, completion on an mbarrier (no multicast).
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0,

@@ -38,25 +38,78 @@ __global__ void __launch_bounds__(256) transpose_cast_kernel(const float* __rest
   }
 }
 
-// Four floats per thread -> four halves (clamped) and four e4m3 bytes (saturating): the operand
-// is read once for both copies.
-__global__ void __launch_bounds__(256) cast_f32_to_f16_e4m3_kernel(const float4* __restrict__ in, uint2* __restrict__ out16,
-                                                                   uint32_t* __restrict__ out8, long long n4) {
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= n4) return;
-  float4 v = in[i];
-  v.x = fminf(fmaxf(v.x, -kHalfMax), kHalfMax);
-  v.y = fminf(fmaxf(v.y, -kHalfMax), kHalfMax);
-  v.z = fminf(fmaxf(v.z, -kHalfMax), kHalfMax);
-  v.w = fminf(fmaxf(v.w, -kHalfMax), kHalfMax);
-  const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
-  uint2 o;
-  o.x = *reinterpret_cast<const uint32_t*>(&h0);
-  o.y = *reinterpret_cast<const uint32_t*>(&h1);
-  out16[i] = o;
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x, v.y), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z, v.w), __NV_SATFINITE, __NV_E4M3);
-  out8[i] = lo | (hi << 16);
+// One warp per row of [rows][ch] f32: four floats per lane and step -> four halves (clamped) and
+// four e4m3 bytes (saturating), so the operand is read once for both copies. The warp also takes
+// the row's sum of squares (each lane adds its elements in order, the lanes are folded by xor
+// shuffles: the same order on every run) and its largest magnitude; stats[0] / stats[1] receive the
+// maxima over all rows as float bits (non-negative floats order like unsigned integers, and a
+// maximum does not depend on the order of the updates). NaN inputs set stats[1] to the NaN pattern.
+__global__ void __launch_bounds__(256) cast_f32_to_f16_e4m3_kernel(const float* __restrict__ in, __half* __restrict__ out16,
+                                                                   uint8_t* __restrict__ out8, long long rows, int ch,
+                                                                   unsigned int* __restrict__ stats) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float4* src = reinterpret_cast<const float4*>(in + row * ch);
+  uint2* dst16 = reinterpret_cast<uint2*>(out16 + row * ch);
+  uint32_t* dst8 = reinterpret_cast<uint32_t*>(out8 + row * ch);
+  float ss = 0.0f, amax = 0.0f;
+  bool bad = false;
+  for (int i = lane; i < ch / 4; i += 32) {
+    float4 v = src[i];
+    ss = fmaf(v.x, v.x, ss);
+    ss = fmaf(v.y, v.y, ss);
+    ss = fmaf(v.z, v.z, ss);
+    ss = fmaf(v.w, v.w, ss);
+    amax = fmaxf(fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y))), fmaxf(fabsf(v.z), fabsf(v.w)));
+    bad = bad || !(v.x == v.x) || !(v.y == v.y) || !(v.z == v.z) || !(v.w == v.w);
+    v.x = fminf(fmaxf(v.x, -kHalfMax), kHalfMax);
+    v.y = fminf(fmaxf(v.y, -kHalfMax), kHalfMax);
+    v.z = fminf(fmaxf(v.z, -kHalfMax), kHalfMax);
+    v.w = fminf(fmaxf(v.w, -kHalfMax), kHalfMax);
+    const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t*>(&h0);
+    o.y = *reinterpret_cast<const uint32_t*>(&h1);
+    dst16[i] = o;
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x, v.y), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z, v.w), __NV_SATFINITE, __NV_E4M3);
+    dst8[i] = lo | (hi << 16);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  }
+  bad = __any_sync(0xffffffffu, bad);
+  if (lane == 0) {
+    atomicMax(stats + 0, __float_as_uint(ss));  // +inf orders above every finite value
+    atomicMax(stats + 1, bad ? 0x7fc00000u : __float_as_uint(amax));
+  }
+}
+
+// Decides, from the operands' statistics alone, whether row maxima taken from the e4m3 copies of Q
+// and K are close enough to the true ones. An e4m3 value differs from the half it was rounded from
+// by a factor within 1 +- 2^-4 (3 mantissa bits) or, below the smallest normal 2^-6, by at most
+// 2^-10; so for every score |q8 . k8 - q . k| <= (2 e + e^2) |q| |k| + d (|q| + |k|) sqrt(n) + n d^2
+// with e = 2^-4, d = 2^-10, n = head_dim (Cauchy-Schwarz). Let E be that bound in the units of the
+// exp2 argument. The half exponentials tolerate a subtracted maximum that is up to 15 too small
+// (the largest is then 2^15) but only about 6 too large (smaller terms start to vanish), so the
+// estimate is used for E <= 10.5 after lowering it by max(0, E - 6): the largest exponential of a
+// row then lies in [2^-6, 2^15]. Otherwise (or when a value exceeds e4m3's largest, 448, or is not
+// a number) gate[0] = 1 and the row maxima come from the half operands, exactly. The decision is a
+// function of the data only, so repeated runs take the same route. gate[1] receives the amount (in
+// raw score units, as float bits) by which the exp epilogue lowers the maxima it subtracts.
+__global__ void wide_gate_kernel(const unsigned int* __restrict__ stats_q, const unsigned int* __restrict__ stats_k,
+                                 int head_dim, float exp_scale, unsigned int* __restrict__ gate) {
+  const float nq = sqrtf(__uint_as_float(stats_q[0])), nk = sqrtf(__uint_as_float(stats_k[0]));
+  const float aq = __uint_as_float(stats_q[1]), ak = __uint_as_float(stats_k[1]);
+  const float e = 0.0625f, d = 0.0009765625f, n = static_cast<float>(head_dim);
+  const float err = (2.0f * e + e * e) * nq * nk + d * (nq + nk) * sqrtf(n) + n * d * d;
+  const float bound = err * exp_scale;
+  const bool safe = (aq <= 448.0f) && (ak <= 448.0f) && (bound <= 10.5f);  // false for NaN
+  gate[0] = safe ? 0u : 1u;
+  gate[1] = __float_as_uint(safe ? fmaxf(bound - 6.0f, 0.0f) / exp_scale : 0.0f);
 }
 
 // One warp per row: lane l adds partial[l], partial[l + 32], ... in order, then the lanes are
@@ -70,7 +123,7 @@ __global__ void __launch_bounds__(256) row_sum_inverse_kernel(const float* __res
   for (int i = lane; i < n_partial; i += 32) s += partial[row * n_partial + i];
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) inv[row] = 1.0f / s;
+  if (lane == 0) inv[row] = s > 0.0f ? 1.0f / s : 0.0f;  // an empty row yields zeros, not NaN
 }
 
 }  // namespace
@@ -81,12 +134,18 @@ cudaError_t launch_transpose_cast(cudaStream_t stream, const float* in, void* ou
   return cudaGetLastError();
 }
 
-cudaError_t launch_cast_f32_to_f16_e4m3(cudaStream_t stream, const float* in, void* out_f16, void* out_e4m3, long long n) {
-  if (n <= 0) return cudaSuccess;
-  if (n % 4 != 0) return cudaErrorInvalidValue;
-  const long long n4 = n / 4;
-  cast_f32_to_f16_e4m3_kernel<<<static_cast<unsigned>((n4 + 255) / 256), 256, 0, stream>>>(
-      reinterpret_cast<const float4*>(in), static_cast<uint2*>(out_f16), static_cast<uint32_t*>(out_e4m3), n4);
+cudaError_t launch_cast_f32_to_f16_e4m3(cudaStream_t stream, const float* in, void* out_f16, void* out_e4m3, long long rows,
+                                        int ch, unsigned int* stats) {
+  if (rows <= 0) return cudaSuccess;
+  if (ch % 4 != 0) return cudaErrorInvalidValue;
+  cast_f32_to_f16_e4m3_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, stream>>>(
+      in, static_cast<__half*>(out_f16), static_cast<uint8_t*>(out_e4m3), rows, ch, stats);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wide_gate(cudaStream_t stream, const unsigned int* stats_q, const unsigned int* stats_k, int head_dim,
+                             float exp_scale, unsigned int* gate) {
+  wide_gate_kernel<<<1, 1, 0, stream>>>(stats_q, stats_k, head_dim, exp_scale, gate);
   return cudaGetLastError();
 }
 

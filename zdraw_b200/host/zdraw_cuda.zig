@@ -195,6 +195,16 @@ pub extern fn zdraw_cuda_static_last_status(stream: ?*anyopaque, status: *u32) c
 // Debugging: pipeline clock stamps of one CTA into a device buffer of >= 1600 u64 words (null = off).
 pub extern fn zdraw_cuda_attn_set_trace(ctx: *anyopaque, device_words: ?*anyopaque, n_words: usize) c_int;
 pub extern fn zdraw_cuda_last_status(ctx: *anyopaque, stream: ?*anyopaque, status: *u32) c_int;
+// Route of the last wide attention call's row maxima: 0 = e4m3 estimate (proven bound), 1 = half operands.
+pub extern fn zdraw_cuda_wide_attention_route(ctx: *anyopaque, stream: ?*anyopaque, exact_row_max: *u32) c_int;
+// Self-test: bounded waits that run out after limit_ns (<= 100 ms) and set bit 8 of the status word.
+pub extern fn zdraw_cuda_selftest_wait_timeout(ctx: *anyopaque, stream: ?*anyopaque, limit_ns: u64) c_int;
+// Head sharding over the GPUs of a node: gather targets of the attention epilogue, shared device memory.
+pub extern fn zdraw_cuda_attn_set_gather(ctx: *anyopaque, n_targets: u32, targets: ?[*]const ?*anyopaque, total_heads: u32, first_head: u32) c_int;
+pub extern fn zdraw_cuda_shared_alloc(ctx: *anyopaque, bytes: usize, dev_ptr: *?*anyopaque, handle64: *[64]u8) c_int;
+pub extern fn zdraw_cuda_shared_free(ctx: *anyopaque, dev_ptr: *anyopaque) c_int;
+pub extern fn zdraw_cuda_shared_open(ctx: *anyopaque, handle64: *const [64]u8, dev_ptr: *?*anyopaque) c_int;
+pub extern fn zdraw_cuda_shared_close(ctx: *anyopaque, dev_ptr: *anyopaque) c_int;
 pub extern fn zdraw_cuda_last_error(ctx: ?*anyopaque) [*:0]const u8;
 pub extern fn zdraw_cuda_klein_rope_table(
     cos_out: [*]f32,

@@ -158,6 +158,11 @@ class Context:
     def shared_free(self, ptr: int) -> None:
         self._check(self._lib.zdraw_cuda_shared_free(self._h, C.c_void_p(ptr)))
 
+    def selftest_wait_timeout(self, limit_ns: int = 2_000_000, stream=None) -> None:
+        """Runs the tiny kernel whose bounded waits run out after ``limit_ns`` and set bit 8 of the
+        context's status word (nothing traps or hangs); see ``zdraw_cuda_selftest_wait_timeout``."""
+        self._check(self._lib.zdraw_cuda_selftest_wait_timeout(self._h, self._stream_ptr(stream), int(limit_ns)))
+
     def reserve(self, params: AttnParams) -> None:
         self._check(self._lib.zdraw_cuda_attn_reserve(self._h, C.byref(params)))
 
@@ -239,6 +244,13 @@ class Context:
             raise UnsupportedShape("wide attention is one head, non-causal")
         self._check(self._lib.zdraw_cuda_wide_attention(self._h, self._stream_ptr(stream), _ptr(q), _ptr(k), _ptr(v),
                                                         _ptr(out), cfg.tokens, cfg.head_dim))
+
+    def wide_attention_route(self, stream=None) -> int:
+        """How the last ``wide_attention`` call took its row maxima: 0 = from the e4m3 copies of q and k
+        (their error proven small from the operands' norms), 1 = from the half operands."""
+        r = C.c_uint32(0)
+        self._check(self._lib.zdraw_cuda_wide_attention_route(self._h, self._stream_ptr(stream), C.byref(r)))
+        return int(r.value)
 
     def klein_rope_table_device(self, txt_len: int, grid_h: int, grid_w: int, ref_h: int = 0, ref_w: int = 0,
                                 theta: float = 2000.0, stream=None):
