@@ -1,7 +1,7 @@
 """Runs the joint-attention path a few times on one synthetic workload (for profilers).
 
-    python -m zdraw_b200.profile_case --workload klein_1024 --iters 4
-    python -m zdraw_b200.profile_case --workload klein_1024 --iters 4 --case linear_qk   (or linear_plain)
+    python profile_case.py --workload klein_1024 --iters 4
+    python profile_case.py --workload klein_1024 --iters 4 --case linear_qk   (or linear_plain, wide)
 
 One untimed call, then `iters` timed ones. Launches per call: qk_norm_rope_kernel, attn_fwd_kernel (plus mask_prepare_kernel with a key
 mask and cast_f32_to_f16_kernel for f32 inputs). Prints the mean device time per iteration.
@@ -12,7 +12,12 @@ import argparse
 
 import torch
 
-from . import mattn, workloads
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from zdraw_b200 import mattn, workloads  # noqa: E402
 
 
 def main() -> None:
@@ -39,7 +44,7 @@ def main() -> None:
 
     flops = w.flops
     if args.case in ("linear_plain", "linear_qk"):
-        from ._lib import LinearParams
+        from zdraw_b200._lib import LinearParams
 
         m, hidden = w.batch * w.tokens, w.heads * 128
         a = torch.randn((m, hidden), device="cuda").half()

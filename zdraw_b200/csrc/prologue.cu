@@ -13,9 +13,12 @@
 //   zflux2_glue_shader.zig:119-120).
 //
 // Mapping: 16 lanes per row, 8 consecutive elements per lane (one 16-byte load for
-// f16 input, two for f32; one 16-byte store); a 16-lane group walks several heads of one
-// token with that token's table and weight slices held in registers. The sum of squares is
-// reduced with xor shuffles in a fixed order, so results are bit-identical run to run.
+// f16 input, two for f32; one 16-byte store); a 16-lane group walks eight heads of one
+// token, all eight rows in flight, with that token's table and weight slices held in
+// registers. The arithmetic runs on packed f32 pairs (fma.rn.f32x2), the inverse norm is
+// rsqrt.approx, and the clamp is the saturating f16x2 conversion: about four instructions per
+// element. The sum of squares is reduced with xor shuffles in a fixed order, so results are
+// bit-identical run to run.
 #include "prologue.cuh"
 
 #include "ptx.cuh"
@@ -30,7 +33,7 @@ namespace {
 
 constexpr int kGroupsPerBlock = 16;  // 16-lane groups per 256-thread block
 constexpr int kHeadsPerGroup = 8;    // heads that share one load of the token's table and weight slices
-constexpr int kRowsInFlight = 4;     // rows loaded before the first is used
+constexpr int kRowsInFlight = 8;     // rows loaded before the first is used: a group's whole chunk
 constexpr float kHalfMax = 65504.0f;
 
 __device__ __forceinline__ void load8(const __half* p, float* x) {
@@ -93,14 +96,19 @@ qk_norm_rope_kernel(const PrologueArgs a, int n_chunks) {
   load8(a.rope_cos + rope_off, cv);
   load8(a.rope_sin + rope_off, sv);
   // y0 = (x0 inv w0) c0 - (x1 inv w1) s0 = inv (x0 (w0 c0) - x1 (w1 s0)), likewise y1: the weight
-  // is folded into the rotation coefficients once per token, not once per head.
-  float ca[8], sb[8];
+  // is folded into the rotation coefficients once per token, not once per head. The arithmetic
+  // runs on packed f32 pairs: the even elements of two rotation pairs in one register pair, the
+  // odd ones in another, so a rotation is two packed multiplies and two packed FMAs per four
+  // elements. ca0/nsb0 give y_even = x_even ca0 + x_odd nsb0, ca1/sb1 give y_odd = x_odd ca1 +
+  // x_even sb1.
+  uint64_t ca0[2], nsb0[2], ca1[2], sb1[2];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    ca[2 * i] = wv[2 * i] * cv[2 * i];              // x0 coefficient of y0
-    sb[2 * i] = wv[2 * i + 1] * sv[2 * i];          // x1 coefficient of y0
-    ca[2 * i + 1] = wv[2 * i + 1] * cv[2 * i + 1];  // x1 coefficient of y1
-    sb[2 * i + 1] = wv[2 * i] * sv[2 * i + 1];      // x0 coefficient of y1
+  for (int j = 0; j < 2; ++j) {  // elements 4j .. 4j+3: pairs (4j, 4j+1) and (4j+2, 4j+3)
+    const int e = 4 * j;
+    ca0[j] = f2_pack(wv[e] * cv[e], wv[e + 2] * cv[e + 2]);
+    nsb0[j] = f2_pack(-(wv[e + 1] * sv[e]), -(wv[e + 3] * sv[e + 2]));
+    ca1[j] = f2_pack(wv[e + 1] * cv[e + 1], wv[e + 3] * cv[e + 3]);
+    sb1[j] = f2_pack(wv[e] * sv[e + 1], wv[e + 2] * sv[e + 3]);
   }
 
   const long long ld = which ? a.ld_k : a.ld_q;
@@ -125,20 +133,35 @@ qk_norm_rope_kernel(const PrologueArgs a, int n_chunks) {
     }
 #pragma unroll
     for (int r = 0; r < kRowsInFlight; ++r) {
-      float ss = 0.0f;
+      uint64_t xe[2], xo[2];  // even / odd elements of the two rotation pairs of each half
 #pragma unroll
-      for (int i = 0; i < 8; ++i) ss = fmaf(x[r][i], x[r][i], ss);
+      for (int j = 0; j < 2; ++j) {
+        xe[j] = f2_pack(x[r][4 * j], x[r][4 * j + 2]);
+        xo[j] = f2_pack(x[r][4 * j + 1], x[r][4 * j + 3]);
+      }
+      uint64_t ss2 = f2_mul(xe[0], xe[0]);
+      ss2 = f2_fma(xo[0], xo[0], ss2);
+      ss2 = f2_fma(xe[1], xe[1], ss2);
+      ss2 = f2_fma(xo[1], xo[1], ss2);
+      float s_lo, s_hi;
+      f2_unpack(ss2, s_lo, s_hi);
+      float ss = s_lo + s_hi;
       // Lanes 0-15 and 16-31 of a warp hold different groups; offsets < 16 keep them apart.
 #pragma unroll
       for (int off = 8; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-      const float inv = 1.0f / sqrtf(ss * (1.0f / 128.0f) + a.eps);
+      // rsqrt.approx is within 2 units in the last place of f32, far below the half rounding of the result.
+      const float inv = rsqrtf(fmaf(ss, 1.0f / 128.0f, a.eps));
+      const uint64_t inv2 = f2_pack(inv, inv);
       uint32_t out[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float x0 = x[r][2 * i], x1 = x[r][2 * i + 1];
-        const float y0 = (x0 * ca[2 * i] - x1 * sb[2 * i]) * inv;
-        const float y1 = (x1 * ca[2 * i + 1] + x0 * sb[2 * i + 1]) * inv;
-        out[i] = pack_clamped(y0, y1);
+      for (int j = 0; j < 2; ++j) {
+        const uint64_t ye = f2_mul(f2_fma(xo[j], nsb0[j], f2_mul(xe[j], ca0[j])), inv2);
+        const uint64_t yo = f2_mul(f2_fma(xe[j], sb1[j], f2_mul(xo[j], ca1[j])), inv2);
+        float e0, e1, o0, o1;
+        f2_unpack(ye, e0, e1);
+        f2_unpack(yo, o0, o1);
+        out[2 * j] = pack_f16x2_sat(e0, o0);      // elements 4j, 4j+1, clamped to +-65504 by the conversion
+        out[2 * j + 1] = pack_f16x2_sat(e1, o1);  // elements 4j+2, 4j+3
       }
       const int h = h0 + r;
       if (live && h < h_end)
