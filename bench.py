@@ -374,7 +374,10 @@ def main():
     ap.add_argument("--shard", default="images", choices=["images", "heads"],
                     help="images: one image per rank (weak scaling); heads: one call's heads split over ranks (strong)")
     ap.add_argument("--allgather", action="store_true",
-                    help="with --shard heads: NCCL all-gather of the head-major outputs inside the step")
+                    help="with --shard heads: gather the head-major outputs of all ranks inside the step")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="how --allgather gathers: peer = stores from the attention epilogue into every rank's "
+                         "buffer + a one-element all-reduce as the fence; nccl = one NCCL all-gather after the kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -435,13 +438,20 @@ def main():
     stream = torch.cuda.current_stream()
     hsl = slice(hs.begin, hs.end)
 
+    peer_gather = None
+    if by_heads and args.allgather and args.gather == "peer":
+        peer_gather = shardlib.PeerGather(ctx, w.batch, w.heads, w.tokens, rank, world)
+        ctx.set_gather(peer_gather.targets, w.heads, hs.begin)
+
     def step(i):
         x = sets[i % n_sets]
         # A head shard is a column slice: same token stride, pointer offset h0 * 128.
         ctx.joint_attention(x["q"][:, :, hsl], x["k"][:, :, hsl], x["v"][:, :, hsl], x["q_w_txt"], x["q_w_img"],
                             x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"], outs[i % n_sets], p,
                             key_mask=x["key_mask"], stream=stream)
-        if by_heads and args.allgather:
+        if peer_gather is not None:
+            peer_gather.fence()
+        elif by_heads and args.allgather:
             shardlib.all_gather_heads(outs[i % n_sets][0], w.heads, rank, world)
 
     launches_per_step = 2 + (1 if w.masked_text is not None else 0) + (1 if w.dtype == "f32" else 0)
@@ -462,6 +472,10 @@ def main():
     ms_total = ev0.elapsed_time(ev1)
     if ctx.last_status() != 0:
         raise SystemExit("a kernel reported a non-zero status during the timed region")
+    if peer_gather is not None:
+        ctx.set_gather(None)
+        peer_gather.close()
+        peer_gather = None
 
     # ---- attention kernel alone (dominant kernel) and prologue alone
     q16 = [torch.empty((w.batch, hs.count, w.tokens, 128), dtype=torch.float16, device="cuda") for _ in range(n_sets)]
@@ -604,13 +618,21 @@ def main():
         for n in ("q", "k", "v"):
             xh[n] = xh[n][:, :, hsl].contiguous().pin_memory()
     oh = torch.empty(out_shape, dtype=xh["q"].dtype).pin_memory()
-    h2d = sum(xh[n].numel() * xh[n].element_size() for n in xh if xh[n] is not None)
+    # The RoPE tables are built on the device once, outside the step (the reference builds them once
+    # per forward and all 25 attention calls of that forward reuse them): a step uploads q, k, v,
+    # the four weight vectors and the key mask, and reads o back.
+    if w.family == "klein":
+        dev_cos, dev_sin = ctx.klein_rope_table_device(w.txt_len, w.grid_h, w.grid_w, w.ref_h, w.ref_w, w.theta)
+    else:
+        dev_cos, dev_sin = ctx.zimage_rope_table_device(w.grid_h, w.grid_w, w.txt_len, theta=w.theta)
+    ctx.set_device_tables(dev_cos, dev_sin)
+    h2d = sum(xh[n].numel() * xh[n].element_size() for n in xh if xh[n] is not None and not n.startswith("rope_"))
     d2h = oh.numel() * oh.element_size()
     e2e_steps = args.e2e_steps or min(args.steps, 20)
 
     def e2e_step():
         ctx.joint_attention_host(xh["q"], xh["k"], xh["v"], xh["q_w_txt"], xh["q_w_img"], xh["k_w_txt"],
-                                 xh["k_w_img"], xh["rope_cos"], xh["rope_sin"], oh, p_host, key_mask=xh["key_mask"])
+                                 xh["k_w_img"], None, None, oh, p_host, key_mask=xh["key_mask"])
 
     for _ in range(3):
         e2e_step()
@@ -620,6 +642,7 @@ def main():
         e2e_step()  # returns when the result is on the host
     t_e2e = (time.perf_counter() - t0) / e2e_steps
     barrier()
+    ctx.set_device_tables()
     clocks = sampler.stop()
 
     # ---- the metric call split by heads over the ranks (strong scaling), N > 1 only
@@ -653,8 +676,11 @@ def main():
             "data": "synthetic",
             "config": workload_config(w, w.batch) | {
                 "flops_per_step_per_gpu": flops_rank, "step": "qk_norm_rope prologue + attention (joint call)",
-                "sharding": ("heads split over GPUs" + (", NCCL all-gather of O inside the step" if args.allgather
-                             else ", no collective")) if by_heads else "one image (seed) per GPU, no collective",
+                "sharding": ("heads split over GPUs" + ((", O gathered by the attention epilogue's peer stores + a one-element "
+                                                         "all-reduce fence" if args.gather == "peer" else
+                                                         ", NCCL all-gather of O inside the step") if args.allgather
+                                                        else ", no collective")) if by_heads
+                            else "one image (seed) per GPU, no collective",
                 "l2": f"inputs rotate over {n_sets} buffer sets ({n_sets * step_bytes / 1e6:.0f} MB > 126 MB L2)",
             },
             "roofline": {
@@ -674,7 +700,8 @@ def main():
                          "ms_per_launch": ms_prologue, "algorithmic_bytes": prologue_bytes},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e, "steps": e2e_steps,
-                    "api": "zdraw_cuda_joint_attention_host (pinned host buffers)"},
+                    "api": "zdraw_cuda_joint_attention_host (pinned host buffers; RoPE tables built on the device once, "
+                           "outside the step)"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }

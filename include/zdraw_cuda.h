@@ -172,6 +172,17 @@ ZDRAW_CUDA_API int zdraw_cuda_joint_attention_host(void *ctx, const void *q, con
                                     const zdraw_cuda_attn_params *p);
 
 /*
+ * RoPE tables that are already on the device, for the host-buffer joint call: the reference
+ * builds its tables once per forward and every block of that forward reuses them
+ * (src/klein/zflux2_resident.zig:1222-1223, 1345-1355), so a caller builds them once with
+ * zdraw_cuda_*_rope_table_device (or uploads them once) and sets them here; while they are set,
+ * zdraw_cuda_joint_attention_host ignores its rope_cos / rope_sin arguments (they may be NULL)
+ * and uploads no tables (4.7 MB per call at 1024 x 1024). The tables must cover what
+ * rope_batch_stride and tokens of the calls say, and stay valid until unset with (NULL, NULL).
+ */
+ZDRAW_CUDA_API int zdraw_cuda_attn_set_device_tables(void *ctx, const float *cos_dev, const float *sin_dev);
+
+/*
  * The joint call for callers that cannot allocate device memory when they need attention
  * (a render loop whose memory was all reserved up front, a plugin held to a fixed device-memory
  * budget by its host, a process told that an allocation may stall the GPU it shares).

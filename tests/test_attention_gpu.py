@@ -336,3 +336,28 @@ def test_gather_targets_receive_every_tile(ctx):
     for t in targets:
         assert torch.equal(t[:, first:first + w.heads].view(torch.int16), want.view(torch.int16))
         assert bool((t[:, :first].view(torch.uint8) == 0xFF).all()) and bool((t[:, first + w.heads:].view(torch.uint8) == 0xFF).all())
+
+
+def test_host_call_with_device_resident_tables(ctx):
+    """The host-buffer joint call with RoPE tables that are already on the device (built there once, as
+    the reference builds its tables once per forward) gives the bytes of the call that uploads host
+    tables: Klein tables from the device builder equal the host builder's bit for bit."""
+    w = workloads.Workload("host_tables_case", "klein", 1, 8, 512, 24, 24, seed=41)  # S = 1088, 4.4 MB per tensor
+    x = workloads.make_inputs(w, "cpu")
+    p = workloads.params(w)
+    want = torch.empty((w.batch, w.tokens, w.heads, 128), dtype=torch.float16)
+    got = torch.empty_like(want)
+    ctx.joint_attention_host(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                             x["rope_cos"], x["rope_sin"], want, p)
+    cos_d, sin_d = ctx.klein_rope_table_device(w.txt_len, w.grid_h, w.grid_w, theta=w.theta)
+    torch.cuda.synchronize()
+    ctx.set_device_tables(cos_d, sin_d)
+    try:
+        ctx.joint_attention_host(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                                 None, None, got, p)
+    finally:
+        ctx.set_device_tables()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    with pytest.raises(mattn.InvalidShape):  # no tables anywhere
+        ctx.joint_attention_host(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                                 None, None, got, p)

@@ -421,7 +421,8 @@ int zdraw_cuda_joint_attention_host(void* ctx, const void* q, const void* k, con
   Shape s;
   int rc = validate(c, p, &s);
   if (rc) return rc;
-  if (!q || !k || !v || !o || !q_w_txt || !q_w_img || !k_w_txt || !k_w_img || !rope_cos || !rope_sin)
+  const bool dev_tables = c->dev_cos != nullptr;  // tables already on the device: nothing to upload
+  if (!q || !k || !v || !o || !q_w_txt || !q_w_img || !k_w_txt || !k_w_img || (!dev_tables && (!rope_cos || !rope_sin)))
     return fail(c, ZDRAW_CUDA_E_ARG, "null host pointer");
   if (p->has_key_mask && !key_mask) return fail(c, ZDRAW_CUDA_E_ARG, "has_key_mask set but key_mask is null");
   ZD_CUDA(c, cudaSetDevice(c->device));
@@ -436,9 +437,10 @@ int zdraw_cuda_joint_attention_host(void* ctx, const void* q, const void* k, con
   const size_t mask_elems = p->mask_batch_stride ? static_cast<size_t>(p->mask_batch_stride) * s.batch
                                                  : static_cast<size_t>(s.tokens);
   if ((rc = ensure(c, c->st_q, q_bytes)) || (rc = ensure(c, c->st_k, k_bytes)) || (rc = ensure(c, c->st_v, v_bytes)) ||
-      (rc = ensure(c, c->st_o, o_bytes)) || (rc = ensure(c, c->st_w, 4 * kHeadDim * sizeof(float))) ||
-      (rc = ensure(c, c->st_cos, rope_elems * sizeof(float))) ||
-      (rc = ensure(c, c->st_sin, rope_elems * sizeof(float))))
+      (rc = ensure(c, c->st_o, o_bytes)) || (rc = ensure(c, c->st_w, 4 * kHeadDim * sizeof(float))))
+    return rc;
+  if (!dev_tables && ((rc = ensure(c, c->st_cos, rope_elems * sizeof(float))) ||
+                      (rc = ensure(c, c->st_sin, rope_elems * sizeof(float)))))
     return rc;
   if (p->has_key_mask && (rc = ensure(c, c->st_mask, mask_elems * sizeof(float)))) return rc;
   // Lazily made once per context: the copy streams and one event pair per chunk.
@@ -469,8 +471,12 @@ int zdraw_cuda_joint_attention_host(void* ctx, const void* q, const void* k, con
   ZD_CUDA(c, cudaMemcpyAsync(w + kHeadDim, q_w_img, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st_in));
   ZD_CUDA(c, cudaMemcpyAsync(w + 2 * kHeadDim, k_w_txt, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st_in));
   ZD_CUDA(c, cudaMemcpyAsync(w + 3 * kHeadDim, k_w_img, kHeadDim * sizeof(float), cudaMemcpyHostToDevice, st_in));
-  ZD_CUDA(c, cudaMemcpyAsync(c->st_cos.p, rope_cos, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st_in));
-  ZD_CUDA(c, cudaMemcpyAsync(c->st_sin.p, rope_sin, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st_in));
+  const float* d_cos = dev_tables ? c->dev_cos : static_cast<const float*>(c->st_cos.p);
+  const float* d_sin = dev_tables ? c->dev_sin : static_cast<const float*>(c->st_sin.p);
+  if (!dev_tables) {
+    ZD_CUDA(c, cudaMemcpyAsync(c->st_cos.p, rope_cos, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st_in));
+    ZD_CUDA(c, cudaMemcpyAsync(c->st_sin.p, rope_sin, rope_elems * sizeof(float), cudaMemcpyHostToDevice, st_in));
+  }
   if (p->has_key_mask)
     ZD_CUDA(c, cudaMemcpyAsync(c->st_mask.p, key_mask, mask_elems * sizeof(float), cudaMemcpyHostToDevice, st_in));
   for (int ch = 0; ch < n_chunks; ++ch) {
@@ -496,8 +502,7 @@ int zdraw_cuda_joint_attention_host(void* ctx, const void* q, const void* k, con
     const size_t hm_chunk_elems = static_cast<size_t>(hc) * s.tokens * kHeadDim;
     char* d_o = static_cast<char*>(c->st_o.p) +
                 (o_hm ? static_cast<size_t>(s.batch) * h0 * s.tokens * kHeadDim : static_cast<size_t>(h0) * kHeadDim) * out_sz;
-    rc = joint(c, st, dq, dk, dv, w, w + kHeadDim, w + 2 * kHeadDim, w + 3 * kHeadDim,
-               static_cast<const float*>(c->st_cos.p), static_cast<const float*>(c->st_sin.p),
+    rc = joint(c, st, dq, dk, dv, w, w + kHeadDim, w + 2 * kHeadDim, w + 3 * kHeadDim, d_cos, d_sin,
                static_cast<const float*>(c->st_mask.p), d_o, p, sc);
     if (rc) {
       cudaStreamSynchronize(st_in);
@@ -578,6 +583,16 @@ int zdraw_cuda_attention_host(void* ctx, const void* q, const void* k, const voi
   uint32_t status = 0;
   ZD_CUDA(c, cudaMemcpy(&status, c->d_status, sizeof(status), cudaMemcpyDeviceToHost));
   if (status != 0) return fail(c, ZDRAW_CUDA_E_DEVICE, "kernel gave up a bounded wait (status 0x%x)", status);
+  return ZDRAW_CUDA_OK;
+}
+
+int zdraw_cuda_attn_set_device_tables(void* ctx, const float* cos_dev, const float* sin_dev) {
+  Ctx* c = as_ctx(ctx);
+  if (!c) return ZDRAW_CUDA_E_ARG;
+  if ((cos_dev == nullptr) != (sin_dev == nullptr)) return fail(c, ZDRAW_CUDA_E_ARG, "give both tables or neither");
+  if (cos_dev && (!aligned16(cos_dev) || !aligned16(sin_dev))) return fail(c, ZDRAW_CUDA_E_ARG, "table is not 16-byte aligned");
+  c->dev_cos = cos_dev;
+  c->dev_sin = sin_dev;
   return ZDRAW_CUDA_OK;
 }
 

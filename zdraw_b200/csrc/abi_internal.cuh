@@ -48,6 +48,9 @@ struct Ctx {
   Buf wa_q16, wa_k16, wa_vt16, wa_aux, wa_p;  // wide-head attention: half operands, row statistics, exp(scores)
   Buf wa_q8, wa_k8;                            // e4m3 copies of Q and K for the row-max pass
   Buf wa_stats;                                // operand statistics (2 + 2 words) and the row-max route word
+  // Device-resident RoPE tables for the host-buffer joint call (zdraw_cuda_attn_set_device_tables).
+  const float* dev_cos = nullptr;
+  const float* dev_sin = nullptr;
   // Gather targets of the head-sharded call (zdraw_cuda_attn_set_gather); 0 = off.
   int n_gather = 0, gather_heads = 0, gather_head0 = 0;
   void* gather[8] = {};

@@ -290,7 +290,7 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
         const bool exp_mode = part.epilogue == kEpilogueExp;
         // plain: optional factor of this row; exp: x -> exp2(x * c + bias), bias = -max * c
         float mul = 1.0f, bias = 0.0f, psum = 0.0f;
-        bool clamped = false;
+        float top = -INFINITY;  // exp: largest raw score of the columns that exist
         if (exp_mode) {
           mul = part.exp_scale;
           const float shift = part.max_shift ? *part.max_shift : 0.0f;
@@ -329,14 +329,13 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
 #pragma unroll
               for (int i = 0; i < 16; ++i) {
                 // (the subtracted maximum may be an estimate, admitted only with a proven error bound:
-                // a result beyond the half range means that bound was broken, and is reported)
-                float e0 = ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias));
-                float e1 = ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias));
+                // a score whose exponential would leave the half range means that bound was broken;
+                // the largest raw score is tracked for that check, one instruction per pair)
+                float e0 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias)), kHalfMax);
+                float e1 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias)), kHalfMax);
                 if (2 * i >= n_live) e0 = 0.0f;
                 if (2 * i + 1 >= n_live) e1 = 0.0f;
-                clamped = clamped || !(e0 <= kHalfMax) || !(e1 <= kHalfMax);
-                e0 = fminf(e0, kHalfMax);
-                e1 = fminf(e1, kHalfMax);
+                if (2 * i + 1 < n_live) top = max3(top, __uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
                 psum += e0 + e1;  // f32 sum of the unrounded values, as the reference's softmax takes it
                 const __half2 v = __floats2half2_rn(e0, e1);
                 h[i] = *reinterpret_cast<const uint32_t*>(&v);
@@ -358,7 +357,8 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
           }
         }
         if (exp_mode && live) part.row_sum[m * (2 * tiles_n) + 2 * tile_n + hh] = psum;
-        if (exp_mode && live && clamped) atomicOr(a.status, kStExpClamp);
+        // exp2 argument of the largest score: 16 is where the half range ends (NaN also reports).
+        if (exp_mode && live && top > -INFINITY && !(fmaf(top, mul, bias) < 15.99f)) atomicOr(a.status, kStExpClamp);
       } else {
         // qk epilogue: the tile's 256 columns are two heads of this token's projection.
         const long long mm = live ? m : 0;

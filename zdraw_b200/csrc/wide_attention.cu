@@ -43,20 +43,36 @@ __global__ void __launch_bounds__(256) transpose_cast_kernel(const float* __rest
 // the row's sum of squares (each lane adds its elements in order, the lanes are folded by xor
 // shuffles: the same order on every run) and its largest magnitude; stats[0] / stats[1] receive the
 // maxima over all rows as float bits (non-negative floats order like unsigned integers, and a
-// maximum does not depend on the order of the updates). NaN inputs set stats[1] to the NaN pattern.
+// maximum does not depend on the order of the updates): one update per block of eight rows, after
+// the block's warps have met in shared memory (two words that thousands of warps hit directly
+// cost more than the cast itself). NaN inputs set stats[1] to the NaN pattern.
 __global__ void __launch_bounds__(256) cast_f32_to_f16_e4m3_kernel(const float* __restrict__ in, __half* __restrict__ out16,
                                                                    uint8_t* __restrict__ out8, long long rows, int ch,
                                                                    unsigned int* __restrict__ stats) {
-  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
+  __shared__ unsigned int block_stats[2];
+  if (threadIdx.x < 2) block_stats[threadIdx.x] = 0u;
+  __syncthreads();
+  const long long row_raw = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const bool live = row_raw < rows;
+  const long long row = live ? row_raw : rows - 1;  // a repeated row changes no maximum and is not stored
   const int lane = threadIdx.x & 31;
   const float4* src = reinterpret_cast<const float4*>(in + row * ch);
   uint2* dst16 = reinterpret_cast<uint2*>(out16 + row * ch);
   uint32_t* dst8 = reinterpret_cast<uint32_t*>(out8 + row * ch);
   float ss = 0.0f, amax = 0.0f;
   bool bad = false;
-  for (int i = lane; i < ch / 4; i += 32) {
-    float4 v = src[i];
+  const int n4 = ch / 4;
+  // Four loads in flight per lane (512 floats per pass of the warp): the row of the VAE shape in one pass.
+  for (int i0 = lane; i0 < n4; i0 += 128) {
+    float4 vv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + 32 * u < n4) vv[u] = __ldg(src + i0 + 32 * u);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+    const int i = i0 + 32 * u;
+    if (i >= n4) break;
+    float4 v = vv[u];
     ss = fmaf(v.x, v.x, ss);
     ss = fmaf(v.y, v.y, ss);
     ss = fmaf(v.z, v.z, ss);
@@ -71,10 +87,11 @@ __global__ void __launch_bounds__(256) cast_f32_to_f16_e4m3_kernel(const float* 
     uint2 o;
     o.x = *reinterpret_cast<const uint32_t*>(&h0);
     o.y = *reinterpret_cast<const uint32_t*>(&h1);
-    dst16[i] = o;
+    if (live) dst16[i] = o;
     const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v.x, v.y), __NV_SATFINITE, __NV_E4M3);
     const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v.z, v.w), __NV_SATFINITE, __NV_E4M3);
-    dst8[i] = lo | (hi << 16);
+    if (live) dst8[i] = lo | (hi << 16);
+    }
   }
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
@@ -83,9 +100,11 @@ __global__ void __launch_bounds__(256) cast_f32_to_f16_e4m3_kernel(const float* 
   }
   bad = __any_sync(0xffffffffu, bad);
   if (lane == 0) {
-    atomicMax(stats + 0, __float_as_uint(ss));  // +inf orders above every finite value
-    atomicMax(stats + 1, bad ? 0x7fc00000u : __float_as_uint(amax));
+    atomicMax(block_stats + 0, __float_as_uint(ss));  // +inf orders above every finite value
+    atomicMax(block_stats + 1, bad ? 0x7fc00000u : __float_as_uint(amax));
   }
+  __syncthreads();
+  if (threadIdx.x < 2) atomicMax(stats + threadIdx.x, block_stats[threadIdx.x]);
 }
 
 // Decides, from the operands' statistics alone, whether row maxima taken from the e4m3 copies of Q

@@ -199,6 +199,8 @@ pub extern fn zdraw_cuda_last_status(ctx: *anyopaque, stream: ?*anyopaque, statu
 pub extern fn zdraw_cuda_wide_attention_route(ctx: *anyopaque, stream: ?*anyopaque, exact_row_max: *u32) c_int;
 // Self-test: bounded waits that run out after limit_ns (<= 100 ms) and set bit 8 of the status word.
 pub extern fn zdraw_cuda_selftest_wait_timeout(ctx: *anyopaque, stream: ?*anyopaque, limit_ns: u64) c_int;
+// RoPE tables already on the device for zdraw_cuda_joint_attention_host (null, null = unset).
+pub extern fn zdraw_cuda_attn_set_device_tables(ctx: *anyopaque, cos_dev: ?[*]const f32, sin_dev: ?[*]const f32) c_int;
 // Head sharding over the GPUs of a node: gather targets of the attention epilogue, shared device memory.
 pub extern fn zdraw_cuda_attn_set_gather(ctx: *anyopaque, n_targets: u32, targets: ?[*]const ?*anyopaque, total_heads: u32, first_head: u32) c_int;
 pub extern fn zdraw_cuda_shared_alloc(ctx: *anyopaque, bytes: usize, dev_ptr: *?*anyopaque, handle64: *[64]u8) c_int;

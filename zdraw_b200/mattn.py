@@ -158,6 +158,12 @@ class Context:
     def shared_free(self, ptr: int) -> None:
         self._check(self._lib.zdraw_cuda_shared_free(self._h, C.c_void_p(ptr)))
 
+    def set_device_tables(self, cos_dev=None, sin_dev=None) -> None:
+        """RoPE tables already on the device (torch CUDA tensors) for ``joint_attention_host``: while set,
+        that call uploads no tables and ignores its ``rope_cos`` / ``rope_sin`` (pass ``None``). The caller keeps
+        the tensors alive; ``set_device_tables()`` unsets."""
+        self._check(self._lib.zdraw_cuda_attn_set_device_tables(self._h, _ptr(cos_dev), _ptr(sin_dev)))
+
     def selftest_wait_timeout(self, limit_ns: int = 2_000_000, stream=None) -> None:
         """Runs the tiny kernel whose bounded waits run out after ``limit_ns`` and set bit 8 of the
         context's status word (nothing traps or hangs); see ``zdraw_cuda_selftest_wait_timeout``."""
