@@ -361,6 +361,11 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
         if (exp_mode && live && top > -INFINITY && !(fmaf(top, mul, bias) < 15.99f)) atomicOr(a.status, kStExpClamp);
       } else {
         // qk epilogue: the tile's 256 columns are two heads of this token's projection.
+        // Its cos/sin rows are parked in the per-warp block that a plain or exp epilogue of an
+        // earlier tile may still be storing from: wait until the copy engine has read those stores'
+        // source (a no-op when the parts of a launch are ordered q, k, then v, as they are today).
+        if (lane == 0) bulk_wait_group_read<0>();
+        __syncwarp();
         const long long mm = live ? m : 0;
         const int tok = static_cast<int>(mm % a.tokens);
         const int img = static_cast<int>(mm / a.tokens);
