@@ -33,7 +33,8 @@ struct PartSpec {
 int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec* parts, const float* rope_cos,
                const float* rope_sin, const zdraw_cuda_linear_params* p, bool operands_e4m3 = false,
                uint32_t w_k_valid = 0,  // columns of W that exist when fewer than k (A has all k)
-               const unsigned int* gate = nullptr, int gate_run_if = 0) {  // device-side launch gate (linear.cuh)
+               const unsigned int* gate = nullptr, int gate_run_if = 0,  // device-side launch gate (linear.cuh)
+               bool rows_first = false) {  // tile order: across the column blocks of a row block first
   if (!p) return fail(cx, ZDRAW_CUDA_E_ARG, "params is null");
   if (p->reserved != 0 || p->m == 0 || p->n == 0 || p->k == 0) return fail(cx, ZDRAW_CUDA_E_ARG, "zero size or reserved != 0");
   if (p->c_dtype != ZDRAW_DTYPE_F16 && p->c_dtype != ZDRAW_DTYPE_F32) return fail(cx, ZDRAW_CUDA_E_ARG, "bad c_dtype");
@@ -69,6 +70,7 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
   la.status = cx->d_status;
   la.gate = gate;
   la.gate_run_if = gate_run_if;
+  la.rows_first = rows_first ? 1 : 0;
   if (any_qk) {
     if (p->tokens == 0 || p->heads == 0 || p->m % p->tokens != 0 || p->n != p->heads * 128u || p->txt_tokens > p->tokens)
       return fail(cx, ZDRAW_CUDA_E_ARG, "qk epilogue needs m = images * tokens and n = heads * 128");
@@ -236,7 +238,8 @@ int zdraw_cuda_wide_attention(void* ctx, void* stream, const float* q, const flo
   po.c_dtype = ZDRAW_DTYPE_F32;
   PartSpec part_o = {cx->wa_vt16.p, o, 0, nullptr, nullptr};
   part_o.row_scale = row_inv;
-  return run_linear(cx, stream, cx->wa_p.p, 1, &part_o, nullptr, nullptr, &po, false, static_cast<uint32_t>(tokens));
+  return run_linear(cx, stream, cx->wa_p.p, 1, &part_o, nullptr, nullptr, &po, false, static_cast<uint32_t>(tokens),
+                    nullptr, 0, true);
 }
 
 int zdraw_cuda_wide_attention_route(void* ctx, void* stream, uint32_t* exact_row_max) {

@@ -159,7 +159,12 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
       bool ok = *abort_flag == 0u;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
         // Consecutive tiles share the W block (part, tile_n) and walk down the rows: W stays in L2.
-        const int col = tile / tiles_m, tile_m = tile % tiles_m;
+        // With rows_first they share the row block of A instead and walk across the column blocks:
+        // the order for a long-K product whose A is the large operand (P V of the wide attention),
+        // so that the column blocks of a row block read A from L2 at the same time.
+        const int n_cols = tiles_n * a.n_parts;
+        const int col = a.rows_first ? tile % n_cols : tile / tiles_m;
+        const int tile_m = a.rows_first ? tile / n_cols : tile % tiles_m;
         const int tile_n = col % tiles_n;
         const CUtensorMap* tm_w = &maps.w[col / tiles_n];
         const int row_a = (2 * tile_m + static_cast<int>(rank)) * kTM;
@@ -244,7 +249,9 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
     int local = 0;
     bool ok = __all_sync(0xffffffffu, *abort_flag == 0u);  // warp-uniform
     for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++local) {
-      const int col = tile / tiles_m, tile_m = 2 * (tile % tiles_m) + static_cast<int>(rank);
+      const int n_cols = tiles_n * a.n_parts;
+      const int col = a.rows_first ? tile % n_cols : tile / tiles_m;
+      const int tile_m = 2 * (a.rows_first ? tile / n_cols : tile % tiles_m) + static_cast<int>(rank);
       const int tile_n = col % tiles_n;
       const LinearPart& part = a.part[col / tiles_n];
       const int b = local & 1;

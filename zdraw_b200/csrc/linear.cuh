@@ -54,6 +54,9 @@ struct LinearArgs {
   // Lets the host enqueue two alternative launches and a device-side decision pick one.
   const unsigned int* gate;
   int gate_run_if;
+  // Tile order: 0 = down the rows of one column block (W stays in L2), 1 = across the column blocks
+  // of one row block (A stays in L2).
+  int rows_first;
 };
 
 struct LinearMaps {
