@@ -361,3 +361,29 @@ def test_host_call_with_device_resident_tables(ctx):
     with pytest.raises(mattn.InvalidShape):  # no tables anywhere
         ctx.joint_attention_host(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
                                  None, None, got, p)
+
+
+def test_growing_row_maxima_rescale_path_on_both_kernels(ctx, oracle):
+    """Keys whose scores grow from tile to tile (each K/V step raises every row's maximum by far more than
+    the lazy-rescale bound of 2^8), so that every step after the first rescales O and l: the path that is
+    rare with N(0,1) data. Run as a 2-head call (a grid below one wave: the one-tile kernel, whose
+    rescale waits for the previous step's P V) and as a 64-head call with the same first two heads (the
+    two-tile kernel); both against the oracle on the half-rounded operands, and byte-equal to each other."""
+    tokens, big = 640, 64
+    rng = np.random.default_rng(77)
+    def half(a):
+        return a.astype(np.float16).astype(np.float32)
+    q = half(rng.standard_normal((tokens, big, 128)).astype(np.float32) * 0.5)
+    k = rng.standard_normal((tokens, big, 128)).astype(np.float32) * 0.5
+    k *= (1.0 + 40.0 * (np.arange(tokens) // 128))[:, None, None]
+    k = half(k)
+    v = half(rng.standard_normal((tokens, big, 128)).astype(np.float32))
+    small = np.full((tokens, 2, 128), np.nan, np.float32)
+    ctx.run(small, np.ascontiguousarray(q[:, :2]), np.ascontiguousarray(k[:, :2]), np.ascontiguousarray(v[:, :2]),
+            mattn.Config(tokens, 2, 2, 128))
+    large = np.full((tokens, big, 128), np.nan, np.float32)
+    ctx.run(large, q, k, v, mattn.Config(tokens, big, big, 128))
+    want = oracle.sdpa(q[:, :2], k[:, :2], v[:, :2], 2)
+    err = np.abs(small - want)
+    assert err.max() <= 2e-2 and err.mean() <= 2e-3, (err.max(), err.mean())
+    np.testing.assert_array_equal(small, large[:, :2])

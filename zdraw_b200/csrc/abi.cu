@@ -290,7 +290,7 @@ int run_attention(Ctx* c, cudaStream_t stream, const void* q16, const void* k16,
   }
   a.status = c->d_status;
   a.trace = c->d_trace;
-  ZD_CUDA(c, zdraw::launch_attn_fwd(stream, tm_q, tm_k, tm_v, tm_o, a));
+  ZD_CUDA(c, zdraw::launch_attn_fwd(stream, tm_q, tm_k, tm_v, tm_o, a, c->sm_count));
   return ZDRAW_CUDA_OK;
 }
 

@@ -707,6 +707,505 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------
+// One query tile per CTA, K/V steps interleaved (for calls with at most one query tile per SM).
+//
+// A CTA's time in attn_fwd_kernel is set by the chain S -> softmax -> P -> P V -> next S of a
+// tile, whether it holds one tile or two; a call with fewer CTAs than SMs (a head shard of one
+// image, a small image) gains nothing from idle SMs there. Here a CTA owns ONE 128-row tile and
+// overlaps the steps of that tile instead: three S buffers in TMEM, so that Q K^T of steps j + 1
+// and j + 2 run while step j is in its softmax, and the two softmax warpgroups take the steps in
+// turn (warps 4-7 the even ones, warps 8-11 the odd ones). What stays serial from step to step is
+// short: the running maximum (decided right after the row maximum of a step, handed to the other
+// warpgroup through shared memory) and the running sum (handed over after the exponentials).
+// Every value is computed by the same operations in the same order as in attn_fwd_kernel - the
+// same maximum rule, the same partial sums, O accumulated step by step - so the two kernels give
+// the same bytes.
+//
+// TMEM columns: [0,128) [128,256) [256,384) S/P of steps j mod 3; [384,512) O.
+// Shared memory: Q 32 KB, K ring 3 x 32 KB, V ring 3 x 32 KB, barriers, two 128-float vectors.
+// ---------------------------------------------------------------------------
+constexpr int kS1OffQ = 0;
+constexpr int kS1OffK = kTileBytes;
+constexpr int kS1OffV = kS1OffK + 3 * kTileBytes;
+constexpr int kS1OffBar = kS1OffV + 3 * kTileBytes;
+constexpr int kS1BarQFull = 0;
+constexpr int kS1BarKFull = 1;    // [3]
+constexpr int kS1BarKEmpty = 4;   // [3]
+constexpr int kS1BarVFull = 7;    // [3]
+constexpr int kS1BarVEmpty = 10;  // [3]  (V of step j released = P V of step j complete)
+constexpr int kS1BarSFull = 13;   // [3]
+constexpr int kS1BarPFull = 16;   // [3 buffers][kPieces]
+constexpr int kS1BarOFull = kS1BarPFull + 3 * kPieces;
+constexpr int kS1BarDrain = kS1BarOFull + 1;
+constexpr int kS1NumBars = kS1BarDrain + 1;
+constexpr int kS1OffFlags = kS1OffBar + kS1NumBars * 8;      // u32 abort, u32 tmem base
+constexpr int kS1OffState = (kS1OffFlags + 16 + 15) / 16 * 16;  // float m_ref[128], l_run[128]
+constexpr int kS1SmemBytes = kS1OffState + 2 * kBM * 4 + 1024;  // + alignment slack
+static_assert(kS1SmemBytes <= 227 * 1024, "shared memory budget");
+// Named barriers (ids; 256 threads each: 128 arrive, 128 wait): hand-over of the running maximum
+// and of the running sum to warpgroup w, and the final meeting of both warpgroups.
+constexpr uint32_t kNbMax = 1, kNbSum = 3, kNbFinal = 5, kNbStage = 6;
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_steps_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                      const AttnArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* sbase = smem_raw + (base - raw_addr);
+  volatile uint32_t* flags = reinterpret_cast<volatile uint32_t*>(sbase + kS1OffFlags);
+  volatile uint32_t* abort_flag = flags;
+  volatile float* m_ref = reinterpret_cast<volatile float*>(sbase + kS1OffState);
+  volatile float* l_run = m_ref + kBM;
+  auto bar = [&](int i) -> uint32_t { return base + kS1OffBar + 8u * static_cast<uint32_t>(i); };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q_tile = blockIdx.x;
+  const int head = blockIdx.y;
+  const int img = blockIdx.z;
+
+  if (threadIdx.x == 0) {
+    flags[0] = (*reinterpret_cast<volatile uint32_t*>(a.status) != 0u) ? 1u : 0u;
+    flags[1] = 0u;
+    mbar_init(bar(kS1BarQFull), 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(bar(kS1BarKFull + s), 1);
+      mbar_init(bar(kS1BarKEmpty + s), 1);
+      mbar_init(bar(kS1BarVFull + s), 1);
+      mbar_init(bar(kS1BarVEmpty + s), 1);
+      mbar_init(bar(kS1BarSFull + s), 1);
+      for (int i = 0; i < kPieces; ++i) mbar_init(bar(kS1BarPFull + kPieces * s + i), kBM);
+    }
+    mbar_init(bar(kS1BarOFull), 1);
+    mbar_init(bar(kS1BarDrain), 1);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  if (*abort_flag) return;
+  if (warp == 1) {
+    tmem_alloc(base + kS1OffFlags + 4, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = flags[1];
+  grid_dependency_wait();
+
+  auto c1 = [&](int hm, int tok) { return hm ? tok : head; };
+  auto c2 = [&](int hm, int tok) { return hm ? head : tok; };
+  const int* tile_list = a.tile_list ? a.tile_list + static_cast<size_t>(img) * a.tile_list_stride : nullptr;
+  const int n_act = tile_list ? tile_list[0] : a.n_kv_tiles;
+  auto tile_entry = [&](int jj) -> int { return tile_list ? tile_list[1 + jj] : jj; };
+
+  if (warp < 4) {
+    reg_dealloc<kRegsControl>();
+    if (warp == 0) {
+      // ---------------------------------------------------------- TMA producer
+      if (lane == 0 && n_act > 0) {
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+        {
+          const int row = q_tile * kBM;
+          mbar_arrive_expect_tx(bar(kS1BarQFull), kTileBytes);
+          tma_load_4d(base + kS1OffQ, &tm_q, bar(kS1BarQFull), 0, c1(a.q_head_major, row), c2(a.q_head_major, row), img);
+          tma_load_4d(base + kS1OffQ + kHalfBytes, &tm_q, bar(kS1BarQFull), 64, c1(a.q_head_major, row),
+                      c2(a.q_head_major, row), img);
+        }
+        bool ok = true;
+        auto load_k = [&](int i) {
+          const uint32_t slot = static_cast<uint32_t>(i) % 3u, phase = (static_cast<uint32_t>(i) / 3u) & 1u;
+          ok = wait_bar(bar(kS1BarKEmpty + slot), phase ^ 1u, abort_flag, a.status, kStProducer);
+          if (!ok) return;
+          const uint32_t dst = base + kS1OffK + slot * kTileBytes;
+          const int row = (tile_entry(i) & kTileIndexMask) * kBN;
+          const int hm = a.k_head_major;
+          mbar_arrive_expect_tx(bar(kS1BarKFull + slot), kTileBytes);
+          tma_load_4d(dst, &tm_k, bar(kS1BarKFull + slot), 0, c1(hm, row), c2(hm, row), img);
+          tma_load_4d(dst + kHalfBytes, &tm_k, bar(kS1BarKFull + slot), 64, c1(hm, row), c2(hm, row), img);
+        };
+        auto load_v = [&](int i) {
+          const uint32_t slot = static_cast<uint32_t>(i) % 3u, phase = (static_cast<uint32_t>(i) / 3u) & 1u;
+          ok = wait_bar(bar(kS1BarVEmpty + slot), phase ^ 1u, abort_flag, a.status, kStProducer);
+          if (!ok) return;
+          const uint32_t dst = base + kS1OffV + slot * kTileBytes;
+          const int row = (tile_entry(i) & kTileIndexMask) * kBN;
+          const int hm = a.v_head_major;
+          mbar_arrive_expect_tx(bar(kS1BarVFull + slot), kTileBytes);
+          tma_load_4d(dst, &tm_v, bar(kS1BarVFull + slot), 0, c1(hm, row), c2(hm, row), img);
+          tma_load_4d(dst + kHalfBytes, &tm_v, bar(kS1BarVFull + slot), 64, c1(hm, row), c2(hm, row), img);
+        };
+        // In the order the MMA warp needs them: K_0, K_1, then K_{i+2} and V_i per step.
+        load_k(0);
+        if (ok && n_act > 1) load_k(1);
+        for (int i = 0; i < n_act && ok; ++i) {
+          if (i + 2 < n_act) load_k(i + 2);
+          if (ok) load_v(i);
+        }
+        if (!ok) {
+          for (int i = 0; i < 100; ++i) __nanosleep(1000);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ---------------------------------------------------------- MMA issuer
+      if (lane == 0 && n_act > 0) {
+        constexpr uint32_t idesc_qk = umma_idesc_f16(kBM, kBN, 0, 0);
+        constexpr uint32_t idesc_pv = umma_idesc_f16(kBM, 128, 0, 1);
+        constexpr uint32_t kHi = kHalfBytes >> 4;  // second 64-column block of a K-major operand (descriptor units)
+        const uint64_t desc_q = smem_desc_sw128(base + kS1OffQ, 16, 1024);
+        const uint32_t d_o = tmem_base + 384u;
+        auto desc_k = [&](int i) { return smem_desc_sw128(base + kS1OffK + (static_cast<uint32_t>(i) % 3u) * kTileBytes, 16, 1024); };
+        auto desc_v = [&](int i) { return smem_desc_sw128(base + kS1OffV + (static_cast<uint32_t>(i) % 3u) * kTileBytes, kHalfBytes, 1024); };
+        auto par3 = [](int i) { return (static_cast<uint32_t>(i) / 3u) & 1u; };
+        // S of step i into buffer i mod 3 (plain form: the first two steps).
+        auto issue_qk = [&](int i) {
+          const uint64_t dk = desc_k(i);
+          const uint32_t d_s = tmem_base + 128u * (static_cast<uint32_t>(i) % 3u);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * kHi + (k & 3) * 2;
+            umma_ss(d_s, desc_q + off, dk + off, idesc_qk, k > 0 ? 1u : 0u);
+          }
+          umma_commit(bar(kS1BarSFull + i % 3));
+          umma_commit(bar(kS1BarKEmpty + i % 3));
+        };
+
+        bool ok = wait_bar(bar(kS1BarQFull), 0, abort_flag, a.status, kStMma);
+        if (ok) ok = wait_bar(bar(kS1BarKFull + 0), 0, abort_flag, a.status, kStMma);
+        if (ok) {
+          tc_fence_after();
+          issue_qk(0);
+        }
+        if (ok && n_act > 1) {
+          ok = wait_bar(bar(kS1BarKFull + 1), 0, abort_flag, a.status, kStMma);
+          if (ok) {
+            tc_fence_after();
+            issue_qk(1);
+          }
+        }
+        // Step j: Q K^T of step j + 2 first (it needs no P), then P V of step j piece by piece.
+        // Every barrier a batch depends on was probed inside the asm block of the batch before it.
+        uint32_t rdy_k = 0;  // K of step j + 2 has landed (probed during step j - 1)
+        for (int j = 0; j < n_act && ok; ++j) {
+          const uint32_t b = static_cast<uint32_t>(j) % 3u, par = par3(j);
+          const uint32_t p_tmem = tmem_base + 128u * b;
+          const uint64_t dv = desc_v(j);
+          uint32_t rdy_v = 0, rdy_p = 0;
+          if (j + 2 < n_act) {
+            const int i = j + 2;
+            if (!rdy_k) {
+              ok = wait_bar(bar(kS1BarKFull + i % 3), par3(i), abort_flag, a.status, kStMma);
+              if (!ok) break;
+            }
+            tc_fence_after();
+            const uint64_t dk = desc_k(i);
+            umma_ss8_probe2(tmem_base + 128u * (static_cast<uint32_t>(i) % 3u), desc_q, dk, idesc_qk, desc_q + kHi, dk + kHi,
+                            bar(kS1BarVFull + b), par, bar(kS1BarPFull + kPieces * b), par, rdy_v, rdy_p);
+            umma_commit(bar(kS1BarSFull + i % 3));
+            umma_commit(bar(kS1BarKEmpty + i % 3));
+          }
+          if (!rdy_v) {
+            ok = wait_bar(bar(kS1BarVFull + b), par, abort_flag, a.status, kStMma);
+            if (!ok) break;
+          }
+          if (!rdy_p) {
+            ok = wait_bar(bar(kS1BarPFull + kPieces * b), par, abort_flag, a.status, kStMma);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          rdy_k = 0;
+#pragma unroll
+          for (int i = 0; i < kPieces; ++i) {
+            const int k0 = piece_begin(i), n = piece_end(i) - piece_begin(i);
+            const uint32_t acc = (j > 0 || i > 0) ? 1u : 0u;
+            // Probed ahead of this piece: the next piece of P, or (last piece) K of step j + 3.
+            const bool last = (i + 1 == kPieces);
+            const bool probe_k = last && (j + 3 < n_act);
+            const uint32_t nb = last ? bar(kS1BarKFull + (j + 3) % 3) : bar(kS1BarPFull + kPieces * b + i + 1);
+            const uint32_t np = last ? par3(j + 3) : par;
+            uint32_t r;
+            if (last && !probe_k) {
+              // nothing left to probe: plain issue
+#pragma unroll
+              for (int k = k0; k < k0 + n; ++k)
+                umma_ts(d_o, p_tmem + 8u * k, dv + 128u * k, idesc_pv, 1u);
+              r = 0;
+            } else {
+              r = (n == 4) ? umma_ts4_probe(d_o, p_tmem + 8u * k0, dv + 128u * k0, idesc_pv, acc, nb, np)
+                           : umma_ts2_probe(d_o, p_tmem + 8u * k0, dv + 128u * k0, idesc_pv, acc, nb, np);
+            }
+            if (last) {
+              rdy_k = probe_k ? r : 0u;
+            } else {
+              if (!r) {
+                ok = wait_bar(nb, np, abort_flag, a.status, kStMma);
+                if (!ok) break;
+              }
+              tc_fence_after();
+            }
+          }
+          if (!ok) break;
+          umma_commit(bar(kS1BarVEmpty + b));  // V slot free; also: P V of step j is complete
+          if (j + 1 == n_act) umma_commit(bar(kS1BarOFull));
+        }
+        if (!ok) {
+          umma_commit(bar(kS1BarDrain));
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(bar(kS1BarDrain), 0) && globaltimer_ns() - t0 < kWaitLimitNs) {
+          }
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    reg_alloc<kRegsSoftmax>();
+    // ------------------------------------------------------------ softmax (steps w, w + 2, ...) + epilogue
+    const int w = (warp - 4) >> 2;          // warpgroup: takes the steps j with j mod 2 == w
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t t_o = tmem_base + 384u + lane_off;
+    const float c = a.scale_log2;
+    const int last_tile = a.n_kv_tiles - 1;
+    const int tail = a.tokens - last_tile * kBN;
+    const float* mask = a.key_mask ? a.key_mask + static_cast<size_t>(img) * a.mask_batch_stride : nullptr;
+    bool ok = true;
+
+    for (int j = w; j < n_act; j += 2) {
+      const uint32_t b = static_cast<uint32_t>(j) % 3u, par = (static_cast<uint32_t>(j) / 3u) & 1u;
+      const uint32_t t_s = tmem_base + 128u * b + lane_off;
+      const bool hand_on = (j + 1 < n_act);  // a next step exists: the other warpgroup waits for this one's state
+      if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kS1BarSFull + b), par, abort_flag, a.status, kStSoftmax));
+      if (!ok) {
+        // A wait ran out somewhere in the CTA: keep the named barriers balanced and do nothing else.
+        if (j > 0) named_barrier_sync(kNbMax + w, 256);
+        if (hand_on) named_barrier_arrive(kNbMax + (1 - w), 256);
+        if (j > 0) named_barrier_sync(kNbSum + w, 256);
+        if (hand_on) named_barrier_arrive(kNbSum + (1 - w), 256);
+        continue;
+      }
+      tc_fence_after();
+      const int entry = tile_entry(j);
+      const int tile = entry & kTileIndexMask;
+      if (entry & kTileMixedFlag) {
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t x[32];
+          tmem_ld_x32(t_s + 32u * ch, x);
+          tmem_wait_ld();
+          const int key0 = tile * kBN + 32 * ch;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + i;
+            const float mv = (key < a.tokens) ? __ldg(mask + key) : -INFINITY;
+            x[i] = __float_as_uint((mv == -INFINITY) ? -INFINITY : fmaf(mv, a.inv_scale, __uint_as_float(x[i])));
+          }
+          tmem_st_x32(t_s + 32u * ch, x);
+          tmem_wait_st();
+        }
+      }
+      uint32_t sr[128];
+      tmem_ld_x32(t_s + 0, sr + 0);
+      tmem_ld_x32(t_s + 32, sr + 32);
+      tmem_ld_x32(t_s + 64, sr + 64);
+      tmem_ld_x32(t_s + 96, sr + 96);
+      tmem_wait_ld();
+      float* s = reinterpret_cast<float*>(sr);
+      if (tile_list == nullptr && tile == last_tile && tail < kBN) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) s[i] = (i < tail) ? s[i] : -INFINITY;
+      }
+      float m_row;
+      {
+        float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+        float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
+#pragma unroll
+        for (int i = 12; i < 124; i += 8) {
+          mx0 = max3(mx0, s[i], s[i + 1]);
+          mx1 = max3(mx1, s[i + 2], s[i + 3]);
+          mx2 = max3(mx2, s[i + 4], s[i + 5]);
+          mx3 = max3(mx3, s[i + 6], s[i + 7]);
+        }
+        mx0 = max3(mx0, s[124], s[125]);
+        mx1 = max3(mx1, s[126], s[127]);
+        m_row = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      }
+      // The running maximum of the steps before comes from the other warpgroup; the rule that
+      // updates it is attn_fwd_kernel's (lazy: only growth beyond 2^8 moves it).
+      float m, alpha = 1.0f;
+      if (j == 0) {
+        m = m_row;
+      } else {
+        named_barrier_sync(kNbMax + w, 256);
+        m = m_ref[row];
+        const bool need = (m_row - m) * c > kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          if (need) {
+            alpha = ex2_approx((m - m_row) * c);
+            m = m_row;
+          }
+          // O holds the steps up to j - 1 once P V of step j - 1 is complete (its V slot is released
+          // by the same commit); P V of step j cannot start before this step hands its P over.
+          const int jp = j - 1;
+          ok = __all_sync(0xffffffffu, wait_bar(bar(kS1BarVEmpty + jp % 3), (static_cast<uint32_t>(jp) / 3u) & 1u,
+                                                abort_flag, a.status, kStSoftmax));
+          if (ok) {
+            tc_fence_after();
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              uint32_t o[32];
+              tmem_ld_x32(t_o + 32u * ch, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st_x32(t_o + 32u * ch, o);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+          }
+        }
+      }
+      m_ref[row] = m;
+      if (hand_on) named_barrier_arrive(kNbMax + (1 - w), 256);
+      if (!ok) {
+        if (j > 0) named_barrier_sync(kNbSum + w, 256);
+        if (hand_on) named_barrier_arrive(kNbSum + (1 - w), 256);
+        continue;
+      }
+
+      const float mc = (m == -INFINITY) ? 0.0f : m * c;
+      const uint64_t c2 = f2_pack(c, c), nmc2 = f2_pack(-mc, -mc);
+      uint64_t acc0 = 0ull, acc1 = 0ull;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int e = 32 * ch + 2 * i;
+          const uint64_t x2 = f2_fma(f2_pack(s[e], s[e + 1]), c2, nmc2);
+          uint64_t p2;
+          if ((i & 3) < kEmuPairsOf4) {
+            p2 = exp2_emulated_pair(x2);
+          } else {
+            float x0, x1;
+            f2_unpack(x2, x0, x1);
+            p2 = f2_pack(ex2_approx(x0), ex2_approx(x1));
+          }
+          if (i & 1) acc1 = f2_add(acc1, p2); else acc0 = f2_add(acc0, p2);
+          float p0, p1;
+          f2_unpack(p2, p0, p1);
+          pk[i] = pack_f16x2(p0, p1);
+        }
+        tmem_st_x16(t_s + 16u * ch, pk);
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+          if (piece_end(i) == 2 * (ch + 1)) {
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(kS1BarPFull + kPieces * b + i));
+          }
+        }
+      }
+      // Running sum: l_j = l_{j-1} * alpha + (this step's sum), each operation rounded by itself as
+      // in attn_fwd_kernel.
+      float a0, a1, b0, b1;
+      f2_unpack(acc0, a0, a1);
+      f2_unpack(acc1, b0, b1);
+      const float step_sum = (a0 + a1) + (b0 + b1);
+      float l = 0.0f;
+      if (j > 0) {
+        named_barrier_sync(kNbSum + w, 256);
+        l = __fmul_rn(l_run[row], alpha);
+      }
+      l = __fadd_rn(l, step_sum);
+      l_run[row] = l;
+      if (hand_on) named_barrier_arrive(kNbSum + (1 - w), 256);
+    }
+
+    // Both warpgroups meet: the running sum of the last step is in shared memory.
+    named_barrier_sync(kNbFinal, 256);
+    if (ok && n_act > 0) ok = __all_sync(0xffffffffu, wait_bar(bar(kS1BarOFull), 0, abort_flag, a.status, kStSoftmax));
+    if (ok) {
+      tc_fence_after();
+      const float l = n_act > 0 ? l_run[row] : 0.0f;
+      const float inv_l = (l > 0.0f) ? 1.0f / l : 0.0f;
+      const int tok = q_tile * kBM + row;
+      const size_t row_off = static_cast<size_t>(img) * a.o_batch_stride + static_cast<size_t>(tok) * a.o_tok_stride +
+                             static_cast<size_t>(head) * a.o_head_stride;
+      // Each warpgroup takes 64 of the 128 output columns: w's half block of the (now free) Q tile.
+      if (a.o_tma && n_act > 0) {
+        uint8_t* qblk = sbase + kS1OffQ + w * kHalfBytes;
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t o[32];
+          tmem_ld_x32(t_o + 64u * w + 32u * ch, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v4;
+            v4.x = pack_f16x2(__uint_as_float(o[8 * i + 0]) * inv_l, __uint_as_float(o[8 * i + 1]) * inv_l);
+            v4.y = pack_f16x2(__uint_as_float(o[8 * i + 2]) * inv_l, __uint_as_float(o[8 * i + 3]) * inv_l);
+            v4.z = pack_f16x2(__uint_as_float(o[8 * i + 4]) * inv_l, __uint_as_float(o[8 * i + 5]) * inv_l);
+            v4.w = pack_f16x2(__uint_as_float(o[8 * i + 6]) * inv_l, __uint_as_float(o[8 * i + 7]) * inv_l);
+            const int jp = 4 * ch + i;  // 16-byte piece of this half's 128-byte row
+            *reinterpret_cast<uint4*>(qblk + row * 128 + ((jp ^ (row & 7)) << 4)) = v4;
+          }
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(kNbStage + static_cast<uint32_t>(w), 128);
+        const int tok0 = q_tile * kBM;
+        if (row == 0) {
+          tma_store_4d(&tm_o, base + kS1OffQ + w * kHalfBytes, 64 * w, c1(a.o_head_major, tok0), c2(a.o_head_major, tok0), img);
+          bulk_commit_group();
+        }
+        if (a.n_gather > 0) {
+          const int rows_valid = min(kBM, a.tokens - tok0);
+          const int piece = static_cast<int>(threadIdx.x) & 7;                 // 16-byte piece of the 128-byte half row
+          const int row_in_pass = (static_cast<int>(threadIdx.x) & 127) >> 3;  // 16 rows per pass
+          const size_t tile_off = ((static_cast<size_t>(img) * a.gather_heads + a.gather_head0 + head) * a.tokens + tok0) * kBM;
+          for (int g = 0; g < a.n_gather; ++g) {
+            __half* dst = static_cast<__half*>(a.gather[g]) + tile_off + 64 * w;
+#pragma unroll 4
+            for (int r0 = 0; r0 < kBM; r0 += 16) {
+              const int r = r0 + row_in_pass;
+              if (r < rows_valid) {
+                const uint4 v4 = *reinterpret_cast<const uint4*>(qblk + r * 128 + ((piece ^ (r & 7)) << 4));
+                *reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * kBM + piece * 8) = v4;
+              }
+            }
+          }
+        }
+        if (row == 0) bulk_wait_group_read<0>();
+      } else {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t o[32];
+          if (n_act > 0) {
+            tmem_ld_x32(t_o + 64u * w + 32u * ch, o);
+            tmem_wait_ld();
+          }
+          if (tok < a.tokens) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = (n_act > 0) ? __uint_as_float(o[i]) * inv_l : 0.0f;
+            store_row_chunk(a, row_off, 64 * w + 32 * ch, v);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------
 // Scalar cross-check kernel: one warp per (image, head, query row), lanes split
 // head_dim, online softmax over keys in order, natural exp. Slow; tests only.
 // It reads the same fp16 q/k/v through the same strides as the tcgen05 kernel.
@@ -818,34 +1317,50 @@ int attn_fwd_trace_words() { return 5 * kTraceIters * kTraceEvents; }
 cudaError_t attn_fwd_configure() {
   // The setmaxnreg budgets assume the registers the CTA is launched with; refuse to run a build
   // whose register count would let an increase wait forever.
-  cudaFuncAttributes attr;
-  cudaError_t e = cudaFuncGetAttributes(&attr, attn_fwd_kernel<false>);
-  if (e != cudaSuccess) return e;
-  if (3 * attr.numRegs < kRegsControl + 2 * kRegsSoftmax) return cudaErrorInvalidConfiguration;
-  e = cudaFuncGetAttributes(&attr, attn_fwd_kernel<true>);
-  if (e != cudaSuccess) return e;
-  if (3 * attr.numRegs < kRegsControl + 2 * kRegsSoftmax) return cudaErrorInvalidConfiguration;
-  e = cudaFuncSetAttribute(attn_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(attn_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  struct K { const void* fn; int smem; };
+  const K kernels[3] = {{reinterpret_cast<const void*>(attn_fwd_kernel<false>), kSmemBytes},
+                        {reinterpret_cast<const void*>(attn_fwd_kernel<true>), kSmemBytes},
+                        {reinterpret_cast<const void*>(attn_fwd_steps_kernel), kS1SmemBytes}};
+  for (const K& k : kernels) {
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, k.fn);
+    if (e != cudaSuccess) return e;
+    if (3 * attr.numRegs < kRegsControl + 2 * kRegsSoftmax) return cudaErrorInvalidConfiguration;
+    e = cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+bool attn_fwd_takes_steps_kernel(int tokens, int heads, int batch, int sm_count, bool traced) {
+  // When every query tile can have an SM of its own, one tile per CTA with its K/V steps
+  // interleaved finishes sooner: a two-tile CTA's time is set by one tile's chain, not by how many
+  // tiles it holds (klein_1024 with 3 heads, 108 tiles: 41 us against 60). With more tiles than SMs
+  // the two-tile kernel's single wave wins again (6 heads, 216 tiles: 81 us against 61).
+  const long long n_q_tiles = (tokens + kBM - 1) / kBM;
+  return !traced && sm_count > 0 && n_q_tiles * heads * batch <= sm_count;
 }
 
 cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
-                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args) {
+                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args, int sm_count) {
   const int n_q_tiles = (args.tokens + kBM - 1) / kBM;
-  dim3 grid((n_q_tiles + 1) / 2, args.heads, args.batch);
   // Programmatic dependent launch: the kernel may become resident while the preceding kernel in
   // the stream drains; it calls griddepcontrol.wait before touching that kernel's results.
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (attn_fwd_takes_steps_kernel(args.tokens, args.heads, args.batch, sm_count, args.trace != nullptr)) {
+    cfg.gridDim = dim3(n_q_tiles, args.heads, args.batch);
+    cfg.dynamicSmemBytes = kS1SmemBytes;
+    return cudaLaunchKernelEx(&cfg, attn_fwd_steps_kernel, tm_q, tm_k, tm_v, tm_o, args);
+  }
+  cfg.gridDim = dim3((n_q_tiles + 1) / 2, args.heads, args.batch);
+  cfg.dynamicSmemBytes = kSmemBytes;
   if (args.trace != nullptr) return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<true>, tm_q, tm_k, tm_v, tm_o, args);
   return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<false>, tm_q, tm_k, tm_v, tm_o, args);
 }

@@ -64,8 +64,11 @@ struct ScalarArgs {
 int attn_fwd_smem_bytes();
 int attn_fwd_trace_words();
 cudaError_t attn_fwd_configure();  // raises the kernel's dynamic shared-memory limit (once per device)
+// sm_count: SMs of the device (0 = unknown). A call with at most one query tile per SM runs on the
+// one-tile kernel that interleaves the K/V steps of a tile; both kernels give the same bytes.
 cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
-                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args);
+                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args, int sm_count);
+bool attn_fwd_takes_steps_kernel(int tokens, int heads, int batch, int sm_count, bool traced);
 cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args);
 // Self-test: one small CTA whose bounded waits run out after limit_ns and set bit 8 of *status.
 cudaError_t launch_wait_timeout_probe(cudaStream_t stream, uint32_t* status, unsigned long long limit_ns);

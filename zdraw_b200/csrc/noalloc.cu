@@ -56,6 +56,7 @@ struct DeviceState {
   bool ready = false;
   unsigned char* scratch = nullptr;  // device address of g_static_scratch on this device
   uint32_t* status = nullptr;        // device address of g_static_status on this device
+  int sm_count = 0;
 };
 
 std::mutex g_mutex;
@@ -79,6 +80,7 @@ int setup_current_device(DeviceState** out) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fail(ZDRAW_CUDA_E_CUDA, "cudaGetDeviceProperties failed");
     if (prop.major != 10) return fail(ZDRAW_CUDA_DECLINED, "device is not sm_100");
+    st.sm_count = prop.multiProcessorCount;
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr)
       return fail(ZDRAW_CUDA_E_CUDA, "cudaGetSymbolAddress(static scratch) failed");
@@ -239,7 +241,7 @@ int zdraw_cuda_joint_attention_static(void* stream, const void* q, const void* k
   a.gather_heads = a.gather_head0 = 0;
   a.status = st->status;
   a.trace = nullptr;
-  if (zdraw::launch_attn_fwd(s, tm_q, tm_k, tm_v, tm_q, a) != cudaSuccess) return fail(ZDRAW_CUDA_E_CUDA, "attention launch failed");
+  if (zdraw::launch_attn_fwd(s, tm_q, tm_k, tm_v, tm_q, a, st->sm_count) != cudaSuccess) return fail(ZDRAW_CUDA_E_CUDA, "attention launch failed");
   return ZDRAW_CUDA_OK;
 }
 

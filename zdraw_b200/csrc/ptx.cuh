@@ -333,6 +333,52 @@ __device__ __forceinline__ void umma_ts2_ss8_probe2(uint32_t d_o, uint32_t a_tme
       : "memory");
 }
 
+// Eight K-steps of S = Q K^T (as in umma_tsN_ss8_probe2, without the P V steps before them), two
+// barriers probed ahead.
+__device__ __forceinline__ void umma_ss8_probe2(uint32_t d_s, uint64_t q_desc, uint64_t k_desc, uint32_t idesc_qk,
+                                                uint64_t q_desc_hi, uint64_t k_desc_hi, uint32_t bar1, uint32_t parity1,
+                                                uint32_t bar2, uint32_t parity2, uint32_t& ready1, uint32_t& ready2) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pw1, pw2, pt, pf;\n\t"
+      ".reg .b64 q1, k1;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pw1, [%6], %7;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 pw2, [%8], %9;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "setp.ne.b32 pf, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], %3, %4, %5, pf;\n\t"
+      "add.u64 q1, %3, 2;\n\t"
+      "add.u64 k1, %4, 2;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], q1, k1, %5, pt;\n\t"
+      "add.u64 q1, %3, 4;\n\t"
+      "add.u64 k1, %4, 4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], q1, k1, %5, pt;\n\t"
+      "add.u64 q1, %3, 6;\n\t"
+      "add.u64 k1, %4, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], q1, k1, %5, pt;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], %10, %11, %5, pt;\n\t"
+      "add.u64 q1, %10, 2;\n\t"
+      "add.u64 k1, %11, 2;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], q1, k1, %5, pt;\n\t"
+      "add.u64 q1, %10, 4;\n\t"
+      "add.u64 k1, %11, 4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], q1, k1, %5, pt;\n\t"
+      "add.u64 q1, %10, 6;\n\t"
+      "add.u64 k1, %11, 6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%2], q1, k1, %5, pt;\n\t"
+      "selp.u32 %0, 1, 0, pw1;\n\t"
+      "selp.u32 %1, 1, 0, pw2;\n\t"
+      "}"
+      : "=r"(ready1), "=r"(ready2)
+      : "r"(d_s), "l"(q_desc), "l"(k_desc), "r"(idesc_qk), "r"(bar1), "r"(parity1), "r"(bar2), "r"(parity2),
+        "l"(q_desc_hi), "l"(k_desc_hi)
+      : "memory");
+}
+// Arrive / wait on a named barrier of the CTA as producer and consumer: `threads` counts both the
+// arriving and the waiting threads.
+__device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 // Tile store shared -> global through a tensor map (completion tracked by bulk groups of the
 // issuing thread). x is the innermost coordinate: x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
