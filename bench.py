@@ -242,8 +242,9 @@ def strong_scaling_record(ctx, rank, world, steps, warmup, stream, barrier, peak
 
     Every rank holds the same inputs (same seed) and computes heads [h0, h1). Timed, max over ranks:
     the shard step without any exchange; with the gather of O done by the attention epilogue (plain
-    stores into every rank's buffer, then a one-element all-reduce as the fence that says all ranks
-    are done); and with one NCCL all-gather after the kernel, for comparison. The gathered O of
+    stores into every rank's buffer, then a one-thread kernel that adds 1 to every rank's arrival
+    counter and polls its own, bounded, as the fence that says all ranks' tiles are here; the same with
+    a one-element all-reduce as the fence); and with one NCCL all-gather after the kernel, for comparison. The gathered O of
     every rank is compared byte for byte with a 1-GPU run of the whole call on that rank: a mismatch
     ends the run. `t1` is that 1-GPU run timed on rank 0 while the other ranks are idle.
     """
@@ -297,19 +298,26 @@ def strong_scaling_record(ctx, rank, world, steps, warmup, stream, barrier, peak
     ms_plain = timed(shard_step)
 
     def gather_step(i):
+        pg.begin_step(hs.begin)
         shard_step(i)
         pg.fence()
 
-    ctx.set_gather(pg.targets, w.heads, hs.begin)
+    def gather_check():
+        # Byte check of the peer-store gather against this rank's own 1-GPU run of the same inputs.
+        pg.poison()
+        barrier()
+        gather_step(0)
+        ctx.set_gather(None)
+        full_step(0)
+        barrier()
+        return bool(torch.equal(pg.local.view(torch.int16), full.view(torch.int16)))
+
     ms_peer = timed(gather_step)
-    # Byte check of the peer-store gather against this rank's own 1-GPU run of the same inputs.
-    pg.local.view(torch.uint8).fill_(0xFF)
-    barrier()
-    gather_step(0)
+    same_peer = gather_check()
+    pg.counters = False  # the same stores, fenced by a one-element all-reduce
+    ms_peer_ar = timed(gather_step)
+    same_peer = gather_check() and same_peer
     ctx.set_gather(None)
-    full_step(0)
-    barrier()
-    same_peer = bool(torch.equal(pg.local.view(torch.int16), full.view(torch.int16)))
 
     def nccl_step(i):
         shard_step(i)
@@ -329,22 +337,27 @@ def strong_scaling_record(ctx, rank, world, steps, warmup, stream, barrier, peak
 
     ms_attn = timed(attn_only)
     status = ctx.last_status()
-    t = torch.tensor([ms_plain, ms_peer, ms_nccl, ms_attn, ms_1, float(not same_peer), float(not same_nccl), float(status)],
-                     dtype=torch.float64, device="cuda")
+    t = torch.tensor([ms_plain, ms_peer, ms_nccl, ms_attn, ms_1, float(not same_peer), float(not same_nccl), float(status),
+                      ms_peer_ar], dtype=torch.float64, device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_plain, ms_peer, ms_nccl, ms_attn, ms_1, bad_peer, bad_nccl, bad_status = t.tolist()
+    ms_plain, ms_peer, ms_nccl, ms_attn, ms_1, bad_peer, bad_nccl, bad_status, ms_peer_ar = t.tolist()
     pg.close()
     if bad_peer or bad_nccl or bad_status:
         raise SystemExit(f"strong-scaling check failed: peer gather mismatch={bool(bad_peer)} nccl gather "
                          f"mismatch={bool(bad_nccl)} status={int(bad_status)}")
     biggest = max(s.count for s in shards)
+    sm_count = torch.cuda.get_device_properties(0).multi_processor_count
+    n_q_tiles = (w.tokens + 127) // 128
+    # at most one query tile per SM: the one-tile kernel (a CTA per tile); else two tiles per CTA
+    ctas = biggest * n_q_tiles if biggest * n_q_tiles <= sm_count else biggest * ((n_q_tiles + 1) // 2)
     attn_tflops = w.flops * biggest / w.heads / (ms_attn * 1e-3) / 1e12
     best = min(ms_peer, ms_nccl)
     return {
         "workload": w.name, "partition": "heads of the one image split contiguously over the GPUs",
-        "heads_per_gpu": [s.count for s in shards], "ctas_per_gpu": biggest * ((w.tokens + 255) // 256),
+        "heads_per_gpu": [s.count for s in shards], "ctas_per_gpu": ctas,
         "ms_per_step_1gpu": ms_1,
-        "ms_per_step": {"no_gather": ms_plain, "gather_by_epilogue_peer_stores": ms_peer, "gather_by_nccl_all_gather": ms_nccl},
+        "ms_per_step": {"no_gather": ms_plain, "gather_by_epilogue_peer_stores": ms_peer,
+                        "gather_by_epilogue_peer_stores_allreduce_fence": ms_peer_ar, "gather_by_nccl_all_gather": ms_nccl},
         "value": w.flops / (best * 1e-3) / 1e12, "unit": "TFLOP/s (whole call, gather included)",
         "speedup_vs_1gpu": {"no_gather": ms_1 / ms_plain, "gather_by_epilogue_peer_stores": ms_1 / ms_peer,
                             "gather_by_nccl_all_gather": ms_1 / ms_nccl},
@@ -353,9 +366,11 @@ def strong_scaling_record(ctx, rank, world, steps, warmup, stream, barrier, peak
         "gather_bytes_received_per_gpu": 2 * w.tokens * 128 * (w.heads - hs.count),
         "attention": {"ms_per_launch": ms_attn, "achieved": attn_tflops, "unit": "TFLOP/s",
                       "frac": attn_tflops / peaks["bf16_tflops"],
-                      "note": "one partial wave: CTAs per GPU against 148 SMs bounds this"},
+                      "note": f"one partial wave: {ctas} CTAs per GPU against {sm_count} SMs bounds this"},
         "byte_check": "gathered O of every rank == the 1-GPU run of the whole call on that rank, byte for byte "
-                      "(both gather forms)",
+                      "(peer stores under either fence, and the NCCL all-gather)",
+        "fence": "a one-thread kernel after the attention kernel adds 1 to every GPU's arrival counter (behind a "
+                 "system-scope fence) and polls its own counter, bounded",
         "l2": f"inputs rotate over {n_sets} buffer sets ({n_sets * shard_bytes / 1e6:.0f} MB of shard operands)",
     }
 
@@ -441,10 +456,11 @@ def main():
     peer_gather = None
     if by_heads and args.allgather and args.gather == "peer":
         peer_gather = shardlib.PeerGather(ctx, w.batch, w.heads, w.tokens, rank, world)
-        ctx.set_gather(peer_gather.targets, w.heads, hs.begin)
 
     def step(i):
         x = sets[i % n_sets]
+        if peer_gather is not None:
+            peer_gather.begin_step(hs.begin)
         # A head shard is a column slice: same token stride, pointer offset h0 * 128.
         ctx.joint_attention(x["q"][:, :, hsl], x["k"][:, :, hsl], x["v"][:, :, hsl], x["q_w_txt"], x["q_w_img"],
                             x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"], outs[i % n_sets], p,
@@ -454,7 +470,8 @@ def main():
         elif by_heads and args.allgather:
             shardlib.all_gather_heads(outs[i % n_sets][0], w.heads, rank, world)
 
-    launches_per_step = 2 + (1 if w.masked_text is not None else 0) + (1 if w.dtype == "f32" else 0)
+    launches_per_step = (2 + (1 if w.masked_text is not None else 0) + (1 if w.dtype == "f32" else 0) +
+                         (1 if peer_gather is not None else 0))  # + the bounded poll of the arrival counter
 
     sampler = ClockSampler(local_rank)
     sampler.start()

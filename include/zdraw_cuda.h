@@ -292,6 +292,29 @@ ZDRAW_CUDA_API int zdraw_cuda_attn_set_gather(void *ctx, uint32_t n_targets, voi
                                               uint32_t total_heads, uint32_t first_head);
 
 /*
+ * Fence of the head-sharded gather, so that no collective has to follow the call. Every GPU of the
+ * group owns one 4-byte arrival counter in its own memory (zero it once); signal[] lists the
+ * counters of all GPUs of the group (peer mappings for the others, the own one included) and `own`
+ * is this GPU's. The call enqueues a one-thread kernel on `stream` that (1) adds 1 to every counter
+ * in signal[] with a release at system scope - the kernels before it in the stream are complete by
+ * then, their stores into the other GPUs' gathered buffers included - and (2) polls `own` (acquire,
+ * system scope; wrap-around compare) until it has reached `target`: with G GPUs and every GPU
+ * calling this once per step, step n (from 1) is gathered on this GPU when its counter reaches
+ * n * G. The poll is bounded: after limit_ns (0 = 2 s; at most 10 s) it sets bit 9 of the context's
+ * status word and ends; the kernel also ends at once, without signalling, when the status word is
+ * already set (this GPU's stores may be missing; the others then run into their limit and report
+ * too). Reaching the count of step n says that every GPU has finished its attention call of step n,
+ * not that it has finished reading what step n - 1 gathered: alternate two gathered buffers (one
+ * counter serves both) or order the readers otherwise. n_signal = 0 only waits; own = NULL only
+ * signals. Measured on two B200s over NVSwitch (klein_1024, 12 heads per GPU): release-adds at system
+ * scope from inside the attention kernel (one per finished tile) cost 35-47 us per call, this
+ * kernel 7-10 us, a one-element all-reduce by NCCL 13 us.
+ * No counterpart in the reference (single GPU).
+ */
+ZDRAW_CUDA_API int zdraw_cuda_gather_fence(void *ctx, void *stream, uint32_t n_signal, uint32_t *const *signal,
+                                           const uint32_t *own, uint32_t target, uint64_t limit_ns);
+
+/*
  * Device memory that the other processes of the node can map (one process per GPU): a plain
  * cudaMalloc whose CUDA IPC handle (64 bytes) is written to handle64; the other processes pass
  * the handle to zdraw_cuda_shared_open and get a peer mapping to use as a gather target. Free /

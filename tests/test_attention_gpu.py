@@ -4,6 +4,8 @@ Follows the reference's three tiers (src/metal/mattn_test.zig): known answers, a
 matrix at the reference's tolerances, then full-size runs checked on sampled rows with
 byte-identical repeats.
 """
+import time
+
 import numpy as np
 import pytest
 
@@ -336,6 +338,67 @@ def test_gather_targets_receive_every_tile(ctx):
     for t in targets:
         assert torch.equal(t[:, first:first + w.heads].view(torch.int16), want.view(torch.int16))
         assert bool((t[:, :first].view(torch.uint8) == 0xFF).all()) and bool((t[:, first + w.heads:].view(torch.uint8) == 0xFF).all())
+
+
+def test_gather_fence_signals_counters_and_its_poll_is_bounded(ctx):
+    """The one-thread fence kernel of the head-sharded gather on one GPU: it adds 1 to every counter it is
+    given and passes once its own counter has reached the target; a target nothing will reach makes it
+    give up at its limit and set bit 9 of the status word (nothing hangs or faults), and while the word
+    is set it neither signals nor waits."""
+    flags = torch.zeros((3, 64), dtype=torch.int32, device="cuda")  # three "GPUs", a counter each on its own lines
+    ptrs = [flags[i].data_ptr() for i in range(3)]
+    try:
+        for n in (1, 2):
+            ctx.gather_fence(ptrs, ptrs[0], n)  # the own counter reaches n by this very call
+            torch.cuda.synchronize()
+            assert flags[:, 0].tolist() == [n, n, n]
+            assert ctx.last_status() == 0
+        ctx.gather_fence(ptrs[1:], None, 0)  # signal only
+        ctx.gather_fence([], ptrs[1], 3)     # wait only, already there
+        torch.cuda.synchronize()
+        assert flags[:, 0].tolist() == [2, 3, 3] and ctx.last_status() == 0
+        # A count that nothing will reach: the poll gives up after 2 ms.
+        t0 = time.perf_counter()
+        ctx.gather_fence([], ptrs[0], 3, limit_ns=2_000_000)
+        ctx.gather_fence(ptrs, ptrs[0], 3)  # status is set: returns at once, signals nothing
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 1.0
+        assert flags[:, 0].tolist() == [2, 3, 3]
+        assert ctx.last_status() == 0x200
+        assert ctx.last_status() == 0
+        # wrap-around compare: a counter just past 2^32 has reached a target just below it
+        flags[0, 0] = 5
+        ctx.gather_fence([], ptrs[0], 0xFFFFFFF0, limit_ns=2_000_000)
+        torch.cuda.synchronize()
+        assert ctx.last_status() == 0
+        with pytest.raises(mattn.InvalidShape):
+            ctx.gather_fence([], None, 1)
+        with pytest.raises(mattn.InvalidShape):
+            ctx.gather_fence(ptrs, ptrs[0], 1, limit_ns=11_000_000_000)
+    finally:
+        ctx.last_status()
+
+
+@pytest.mark.parametrize("heads", [2, 50])  # 6 query tiles: the one-tile kernel; 150: the two-tile kernel
+def test_gather_targets_get_zeros_when_every_key_is_masked(ctx, heads):
+    """An image whose keys are all masked is written as zeros - into the gather targets too."""
+    w = workloads.Workload("gather_masked_case", "klein", 1, heads, 256, 4, 4, seed=35)  # S = 272
+    x = workloads.make_inputs(w, "cuda")
+    p = workloads.params(w, out_layout=_lib.LAYOUT_HEAD_MAJOR, has_key_mask=1)
+    mask = torch.full((w.tokens,), float("-inf"), dtype=torch.float32, device="cuda")
+    target = torch.empty((w.batch, w.heads, w.tokens, 128), dtype=torch.float16, device="cuda")
+    target.view(torch.uint8).fill_(0xFF)
+    got = torch.empty_like(target)
+    got.view(torch.uint8).fill_(0xFF)
+    try:
+        ctx.set_gather([target.data_ptr()], w.heads, 0)
+        ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
+                            x["rope_cos"], x["rope_sin"], got, p, key_mask=mask)
+        torch.cuda.synchronize()
+        assert ctx.last_status() == 0
+    finally:
+        ctx.set_gather(None)
+    assert not got.view(torch.int16).any() and not target.view(torch.int16).any()
 
 
 def test_host_call_with_device_resident_tables(ctx):

@@ -82,6 +82,7 @@ SYMBOLS = {
     "zdraw_cuda_zimage_rope_table_device": (C.c_int, [_VP] * 4 + [C.c_size_t] * 4 + [_VP, _VP, C.c_float]),
     "zdraw_cuda_attn_set_device_tables": (C.c_int, [_VP, _VP, _VP]),
     "zdraw_cuda_attn_set_gather": (C.c_int, [_VP, C.c_uint32, C.POINTER(C.c_void_p), C.c_uint32, C.c_uint32]),
+    "zdraw_cuda_gather_fence": (C.c_int, [_VP, _VP, C.c_uint32, C.POINTER(C.c_void_p), _VP, C.c_uint32, C.c_uint64]),
     "zdraw_cuda_shared_alloc": (C.c_int, [_VP, C.c_size_t, C.POINTER(C.c_void_p), _VP]),
     "zdraw_cuda_shared_free": (C.c_int, [_VP, _VP]),
     "zdraw_cuda_shared_open": (C.c_int, [_VP, _VP, C.POINTER(C.c_void_p)]),

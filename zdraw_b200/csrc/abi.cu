@@ -616,6 +616,23 @@ int zdraw_cuda_attn_set_gather(void* ctx, uint32_t n_targets, void* const* targe
   return ZDRAW_CUDA_OK;
 }
 
+int zdraw_cuda_gather_fence(void* ctx, void* stream, uint32_t n_signal, uint32_t* const* signal, const uint32_t* own,
+                            uint32_t target, uint64_t limit_ns) {
+  Ctx* c = as_ctx(ctx);
+  if (!c) return ZDRAW_CUDA_E_ARG;
+  if (n_signal > static_cast<uint32_t>(zdraw::kMaxGather) || (n_signal > 0 && !signal) || (n_signal == 0 && !own))
+    return fail(c, ZDRAW_CUDA_E_ARG, "gather fence: at most %d counters to signal, or one to wait on", zdraw::kMaxGather);
+  for (uint32_t i = 0; i < n_signal; ++i)
+    if (!signal[i] || (reinterpret_cast<uintptr_t>(signal[i]) & 3u)) return fail(c, ZDRAW_CUDA_E_ARG, "counter %u is null or misaligned", i);
+  if (own && (reinterpret_cast<uintptr_t>(own) & 3u)) return fail(c, ZDRAW_CUDA_E_ARG, "own counter is misaligned");
+  if (limit_ns == 0) limit_ns = 2000ull * 1000ull * 1000ull;
+  if (limit_ns > 10000ull * 1000ull * 1000ull) return fail(c, ZDRAW_CUDA_E_ARG, "limit_ns above 10 s");
+  ZD_CUDA(c, cudaSetDevice(c->device));
+  ZD_CUDA(c, zdraw::launch_gather_fence(static_cast<cudaStream_t>(stream), static_cast<int>(n_signal), signal, own, target,
+                                        c->d_status, limit_ns));
+  return ZDRAW_CUDA_OK;
+}
+
 // Device memory that other processes of the node can map: plain cudaMalloc (so that an IPC handle
 // names exactly this allocation), exported and opened with the CUDA IPC calls.
 int zdraw_cuda_shared_alloc(void* ctx, size_t bytes, void** dev_ptr, void* handle64) {

@@ -102,6 +102,7 @@ constexpr uint32_t kStProducer = 1u << 0;
 constexpr uint32_t kStMma = 1u << 1;
 constexpr uint32_t kStSoftmax = 1u << 2;
 constexpr uint32_t kStWaitProbe = 1u << 8;  // the self-test kernel below
+constexpr uint32_t kStGatherWait = 1u << 9;  // gather_fence_kernel's poll gave up
 
 // Tile-list entries: K/V tile index, plus a flag for tiles the key mask covers partly.
 constexpr int kTileMixedFlag = 0x40000000;
@@ -692,6 +693,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             store_row_chunk(a, row_off, 32 * ch, v);
           }
         }
+        if (a.n_gather > 0 && a.o_tma && tok < a.tokens) {
+          // Every key masked: the targets get the row of zeros too.
+          const size_t dst_off = ((static_cast<size_t>(img) * a.gather_heads + a.gather_head0 + head) * a.tokens + tok) * kBM;
+          for (int g = 0; g < a.n_gather; ++g) {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(a.gather[g]) + dst_off);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
       }
     }
   }
@@ -1196,6 +1206,15 @@ attn_fwd_steps_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
             store_row_chunk(a, row_off, 64 * w + 32 * ch, v);
           }
         }
+        if (a.n_gather > 0 && a.o_tma && tok < a.tokens) {
+          // Every key masked: the targets get this warpgroup's half row of zeros too.
+          const size_t dst_off = ((static_cast<size_t>(img) * a.gather_heads + a.gather_head0 + head) * a.tokens + tok) * kBM + 64 * w;
+          for (int g = 0; g < a.n_gather; ++g) {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(a.gather[g]) + dst_off);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
       }
     }
   }
@@ -1363,6 +1382,52 @@ cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const 
   cfg.dynamicSmemBytes = kSmemBytes;
   if (args.trace != nullptr) return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<true>, tm_q, tm_k, tm_v, tm_o, args);
   return cudaLaunchKernelEx(&cfg, attn_fwd_kernel<false>, tm_q, tm_k, tm_v, tm_o, args);
+}
+
+// Fence of the head-sharded gather, one thread: tells every GPU of the group that this GPU's
+// kernels before it in the stream are complete (their stores into the gathered buffers included:
+// a kernel boundary orders them) by adding 1 to each GPU's arrival counter behind a fence at system
+// scope, then polls its own counter (acquire, system scope) until it has reached `target`
+// (wrap-around compare) or limit_ns have passed, which sets kStGatherWait.
+struct GatherFenceArgs {
+  uint32_t* signal[kMaxGather];
+  int n_signal;
+  const uint32_t* own;
+  uint32_t target;
+  uint32_t* status;
+  unsigned long long limit_ns;
+};
+__global__ void gather_fence_kernel(const GatherFenceArgs a) {
+  if (ld_volatile_u32(a.status) != 0u) return;  // an earlier kernel gave up: its stores may be missing
+  if (a.n_signal > 0) {
+    __threadfence_system();  // one fence orders everything before it ahead of all the additions
+    for (int i = 0; i < a.n_signal; ++i) red_add_relaxed_sys(a.signal[i], 1u);
+  }
+  if (a.own == nullptr) return;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+    const uint32_t v = ld_acquire_sys_u32(a.own);
+    if (static_cast<int32_t>(v - a.target) >= 0) return;
+    if (globaltimer_ns() - t0 > a.limit_ns) {
+      atomicOr(a.status, kStGatherWait);
+      return;
+    }
+    __nanosleep(64);
+  }
+}
+
+cudaError_t launch_gather_fence(cudaStream_t stream, int n_signal, uint32_t* const* signal, const uint32_t* own,
+                                uint32_t target, uint32_t* status, unsigned long long limit_ns) {
+  GatherFenceArgs a{};
+  if (n_signal < 0 || n_signal > kMaxGather) return cudaErrorInvalidValue;
+  for (int i = 0; i < n_signal; ++i) a.signal[i] = signal[i];
+  a.n_signal = n_signal;
+  a.own = own;
+  a.target = target;
+  a.status = status;
+  a.limit_ns = limit_ns;
+  gather_fence_kernel<<<1, 1, 0, stream>>>(a);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_wait_timeout_probe(cudaStream_t stream, uint32_t* status, unsigned long long limit_ns) {

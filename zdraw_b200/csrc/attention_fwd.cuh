@@ -72,6 +72,12 @@ bool attn_fwd_takes_steps_kernel(int tokens, int heads, int batch, int sm_count,
 cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args);
 // Self-test: one small CTA whose bounded waits run out after limit_ns and set bit 8 of *status.
 cudaError_t launch_wait_timeout_probe(cudaStream_t stream, uint32_t* status, unsigned long long limit_ns);
+// Fence of the head-sharded gather: one thread adds 1 (release, system scope) to each of the n_signal
+// counters - one in every GPU's memory - and then polls `own` (acquire, system scope) until it has
+// reached `target` (wrap-around compare) or limit_ns have passed; then it sets bit 9 of *status.
+// Does nothing if *status is already set. own == nullptr: signal only.
+cudaError_t launch_gather_fence(cudaStream_t stream, int n_signal, uint32_t* const* signal, const uint32_t* own,
+                                uint32_t target, uint32_t* status, unsigned long long limit_ns);
 // Classifies the K/V tiles of each image under `key_mask` and writes the tile lists
 // (1 + n_kv_tiles ints per image, `list_stride` ints apart).
 cudaError_t launch_mask_prepare(cudaStream_t stream, const float* key_mask, long long mask_batch_stride,

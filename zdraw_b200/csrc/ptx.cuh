@@ -374,6 +374,21 @@ __device__ __forceinline__ void umma_ss8_probe2(uint32_t d_s, uint64_t q_desc, u
         "l"(q_desc_hi), "l"(k_desc_hi)
       : "memory");
 }
+// Arrival counter in (possibly another GPU's) global memory: added to behind a system-scope fence,
+// read with acquire at system scope.
+__device__ __forceinline__ void red_add_relaxed_sys(uint32_t* addr, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
 // Arrive / wait on a named barrier of the CTA as producer and consumer: `threads` counts both the
 // arriving and the waiting threads.
 __device__ __forceinline__ void named_barrier_arrive(uint32_t id, uint32_t threads) {

@@ -203,6 +203,8 @@ pub extern fn zdraw_cuda_selftest_wait_timeout(ctx: *anyopaque, stream: ?*anyopa
 pub extern fn zdraw_cuda_attn_set_device_tables(ctx: *anyopaque, cos_dev: ?[*]const f32, sin_dev: ?[*]const f32) c_int;
 // Head sharding over the GPUs of a node: gather targets of the attention epilogue, shared device memory.
 pub extern fn zdraw_cuda_attn_set_gather(ctx: *anyopaque, n_targets: u32, targets: ?[*]const ?*anyopaque, total_heads: u32, first_head: u32) c_int;
+// Fence of the gather: adds 1 to every GPU's arrival counter, then polls the own one (bounded) up to `target`.
+pub extern fn zdraw_cuda_gather_fence(ctx: *anyopaque, stream: ?*anyopaque, n_signal: u32, signal: ?[*]const ?*u32, own: ?*const u32, target: u32, limit_ns: u64) c_int;
 pub extern fn zdraw_cuda_shared_alloc(ctx: *anyopaque, bytes: usize, dev_ptr: *?*anyopaque, handle64: *[64]u8) c_int;
 pub extern fn zdraw_cuda_shared_free(ctx: *anyopaque, dev_ptr: *anyopaque) c_int;
 pub extern fn zdraw_cuda_shared_open(ctx: *anyopaque, handle64: *const [64]u8, dev_ptr: *?*anyopaque) c_int;

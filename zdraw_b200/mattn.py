@@ -141,6 +141,21 @@ class Context:
         arr = (C.c_void_p * max(len(targets), 1))(*[C.c_void_p(int(t)) for t in targets])
         self._check(self._lib.zdraw_cuda_attn_set_gather(self._h, len(targets), arr, int(total_heads), int(first_head)))
 
+    def gather_fence(self, signal, own: int | None, target: int, limit_ns: int = 0, stream=None) -> None:
+        """Enqueues the one-thread fence kernel of the head-sharded gather: adds 1 to each arrival counter in
+        ``signal`` (device pointers as ints, or a prebuilt ctypes array; one counter per GPU of the group) and
+        polls this GPU's counter ``own`` until it reaches ``target`` (modulo 2^32). A poll that runs out sets
+        bit 9 of the status word. See ``zdraw_cuda_gather_fence``."""
+        if isinstance(signal, C.Array):
+            arr, n = signal, len(signal)
+        else:
+            signal = list(signal or [])
+            n = len(signal)
+            arr = (C.c_void_p * max(n, 1))(*[C.c_void_p(int(f)) for f in signal])
+        self._check(self._lib.zdraw_cuda_gather_fence(self._h, self._stream_ptr(stream), n, arr,
+                                                      C.c_void_p(int(own)) if own else None,
+                                                      int(target) & 0xFFFFFFFF, int(limit_ns)))
+
     def shared_alloc(self, nbytes: int):
         """Device memory the node's other processes can map: (device pointer, 64-byte IPC handle)."""
         ptr, handle = C.c_void_p(), C.create_string_buffer(64)

@@ -89,42 +89,79 @@ class _DevicePointer:
 
 
 class PeerGather:
-    """Gathered O buffers of one head-sharded call, one per rank, each mapped into every rank.
+    """Gathered O buffers of a head-sharded call, one set per rank, each mapped into every rank.
 
-    Every rank allocates ``[images, heads, tokens, 128]`` f16 with ``Context.shared_alloc`` (plain
-    ``cudaMalloc`` + CUDA IPC handle), the handles go round with ``all_gather_object`` and every rank
-    opens the others' buffers. ``targets`` is then the list of ``world`` device pointers (own buffer
-    first-class, peers as mappings) for ``Context.set_gather``; ``local`` is this rank's buffer as a
-    torch tensor. The stores of a step are complete on a rank when its stream has passed the call;
-    ``fence`` makes every rank wait until all ranks have got there (a one-element all-reduce).
+    Every rank allocates ``buffers`` tensors ``[images, heads, tokens, 128]`` f16 and one arrival
+    counter with ``Context.shared_alloc`` (plain ``cudaMalloc`` + CUDA IPC handle), the handles go
+    round with ``all_gather_object`` and every rank opens the others' memory. ``begin_step`` points
+    the context at the next buffer of every rank (own memory first-class, peers as mappings); after the
+    attention call ``fence`` enqueues the one-thread kernel that adds 1 to every rank's counter and polls
+    this rank's own, bounded (``Context.gather_fence``): when the stream has passed it, ``local`` holds all
+    heads. With ``counters=False`` the fence is a one-element all-reduce instead. Two buffers (the default)
+    let step n + 1 write while a slow rank still reads what step n gathered.
     """
 
-    def __init__(self, ctx, images: int, heads: int, tokens: int, rank: int, world: int, group=None):
+    def __init__(self, ctx, images: int, heads: int, tokens: int, rank: int, world: int, group=None,
+                 buffers: int = 2, counters: bool = True):
         import torch
         import torch.distributed as dist
 
         self.ctx, self.rank, self.world, self.group = ctx, rank, world, group
         self.shape = (images, heads, tokens, 128)
+        self.buffers, self.counters = int(buffers), bool(counters)
         nbytes = images * heads * tokens * 128 * 2
-        self._own, handle = ctx.shared_alloc(nbytes)
+        self._nbytes = nbytes
+        total = self.buffers * nbytes + 256  # the counter sits behind the buffers, on its own lines
+        self._own, handle = ctx.shared_alloc(total)
         handles = [None] * world
         dist.all_gather_object(handles, handle, group=group)
         self._opened = []
-        self.targets = []
+        self._bases = []
         for r in range(world):
             if r == rank:
-                self.targets.append(self._own)
+                self._bases.append(self._own)
             else:
                 p = ctx.shared_open(handles[r])
                 self._opened.append(p)
-                self.targets.append(p)
-        self.local = torch.as_tensor(_DevicePointer(self._own, self.shape), device=f"cuda:{ctx.device}")
-        self._token = torch.zeros(1, dtype=torch.int32, device=f"cuda:{ctx.device}")
+                self._bases.append(p)
+        dev = f"cuda:{ctx.device}"
+        self._locals = [torch.as_tensor(_DevicePointer(self._own + b * nbytes, self.shape), device=dev)
+                        for b in range(self.buffers)]
+        self._flag_view = torch.as_tensor(_DevicePointer(self._own + self.buffers * nbytes, (64,), "<i4"), device=dev)
+        self._flag_view.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=group)  # every counter is zero before anybody adds to one
+        import ctypes as C
 
-    def fence(self):
-        import torch.distributed as dist
+        self._flags = (C.c_void_p * world)(*[C.c_void_p(base + self.buffers * nbytes) for base in self._bases])
+        self._step = 0
+        self._token = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.local = self._locals[0]
+        self.targets = [base for base in self._bases]
 
-        dist.all_reduce(self._token, group=self.group)
+    def begin_step(self, first_head: int):
+        """Gather targets (and counters) of the next step; returns this rank's buffer of that step."""
+        b = self._step % self.buffers
+        self._step += 1
+        self.targets = [base + b * self._nbytes for base in self._bases]
+        self.ctx.set_gather(self.targets, self.shape[1], first_head)
+        self.local = self._locals[b]
+        return self.local
+
+    def poison(self):
+        """Fills this rank's gathered buffers with 0xFF bytes (f16 NaNs): unwritten tiles show."""
+        import torch
+
+        for t in self._locals:
+            t.view(torch.uint8).fill_(0xFF)
+
+    def fence(self, limit_ns: int = 0):
+        if self.counters:
+            self.ctx.gather_fence(self._flags, self._own + self.buffers * self._nbytes, self._step * self.world, limit_ns)
+        else:
+            import torch.distributed as dist
+
+            dist.all_reduce(self._token, group=self.group)
 
     def close(self):
         import torch
@@ -132,10 +169,13 @@ class PeerGather:
 
         torch.cuda.synchronize()
         dist.barrier(group=self.group)  # nobody still writes into a buffer that is about to go
+        self.ctx.set_gather(None)
         for p in self._opened:
             self.ctx.shared_close(p)
         self._opened = []
         self.local = None
+        self._locals = []
+        self._flag_view = None
         dist.barrier(group=self.group)
         if self._own:
             self.ctx.shared_free(self._own)
