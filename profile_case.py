@@ -2,6 +2,7 @@
 
     python profile_case.py --workload klein_1024 --iters 4
     python profile_case.py --workload klein_1024 --iters 4 --case linear_qk   (or linear_plain, wide)
+    python profile_case.py --workload klein_1024 --iters 4 --heads 3          (a head shard: attn_fwd_steps_kernel)
 
 One untimed call, then `iters` timed ones. Launches per call: qk_norm_rope_kernel, attn_fwd_kernel (plus mask_prepare_kernel with a key
 mask and cast_f32_to_f16_kernel for f32 inputs). Prints the mean device time per iteration.
@@ -25,6 +26,9 @@ def main() -> None:
     ap.add_argument("--workload", default="klein_1024", choices=sorted(workloads.WORKLOADS))
     ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch")
+    ap.add_argument("--heads", type=int, default=0,
+                    help="joint case: run only the first HEADS heads, as a column slice of the full tensors (a head "
+                         "shard; with at most one query tile per SM it runs on attn_fwd_steps_kernel)")
     ap.add_argument("--case", default="joint", choices=["joint", "linear_plain", "linear_qk", "wide"],
                     help="joint: prologue + attention; linear_*: one projection GEMM (linear_kernel) of the "
                          "workload's token count and hidden size, plain f16 store or fused q/k epilogue; "
@@ -38,11 +42,20 @@ def main() -> None:
     x = workloads.make_inputs(w, "cuda")
     p = workloads.params(w)
     out = torch.empty((w.batch, w.tokens, w.heads, 128), dtype=x["q"].dtype, device="cuda")
+    flops = w.flops
+    if args.heads:
+        ld = w.heads * 128
+        p = workloads.params(w, heads=args.heads, ld_q=ld, ld_k=ld, ld_v=ld, ld_o=ld)
+        x = dict(x)
+        for n in ("q", "k", "v"):
+            x[n] = x[n][:, :, :args.heads]
+        out = out[:, :, :args.heads]
+        flops = w.flops * args.heads / w.heads
+
     def call():
         ctx.joint_attention(x["q"], x["k"], x["v"], x["q_w_txt"], x["q_w_img"], x["k_w_txt"], x["k_w_img"],
                             x["rope_cos"], x["rope_sin"], out, p, key_mask=x["key_mask"])
 
-    flops = w.flops
     if args.case in ("linear_plain", "linear_qk"):
         from zdraw_b200._lib import LinearParams
 
