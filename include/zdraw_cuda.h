@@ -52,11 +52,16 @@ extern "C" {
 #define ZDRAW_LAYOUT_TOKEN_MAJOR 0u /* [batch][tokens][heads][D], token stride ld_* elements */
 #define ZDRAW_LAYOUT_HEAD_MAJOR 1u  /* [batch][heads][tokens][D], dense                      */
 
-/* Attention kernels. 0 is the product kernel; 1 is a slow scalar kernel kept to
- * cross-check it in tests (the reference keeps `attention_rows` beside its fast
- * kernels the same way, src/metal/mattn_test.zig:91-128). */
+/* Attention kernels. 0 is the product path: the tcgen05 kernel in its two-tile form, or in its
+ * one-tile form when the call has at most one query tile per SM (both give the same bytes); 1 is
+ * a slow scalar kernel kept to cross-check it in tests (the reference keeps `attention_rows`
+ * beside its fast kernels the same way, src/metal/mattn_test.zig:91-128); 2 and 3 pin the form
+ * of the tcgen05 kernel whatever the size of the call (tests compare the two forms; the
+ * reference's env switches that pin a route, src/metal/mattn.zig:134-150, are the model). */
 #define ZDRAW_KERNEL_TCGEN05 0u
 #define ZDRAW_KERNEL_SCALAR 1u
+#define ZDRAW_KERNEL_TCGEN05_TWO_TILE 2u
+#define ZDRAW_KERNEL_TCGEN05_ONE_TILE 3u
 
 /*
  * Call descriptor. Mirrors AttnParams (src/metal/metal_c.zig:245-256: tokens,

@@ -97,6 +97,11 @@ def test_shape_matrix_matches_cpu(ctx, oracle, tokens, heads):
     ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128))
     assert not np.isnan(got).any()
     assert np.abs(got - want).max() <= 2e-3
+    # Either form of the tcgen05 kernel, pinned: the same bytes as the product's choice.
+    for form in (_lib.KERNEL_TWO_TILE, _lib.KERNEL_ONE_TILE):
+        pinned = np.full_like(q, np.nan)
+        ctx.run(pinned, q, k, v, mattn.Config(tokens, heads, heads, 128), kernel=form)
+        np.testing.assert_array_equal(pinned, got, err_msg=f"kernel form {form}")
     # The scalar kernel on the same inputs agrees with both.
     ref = np.full_like(q, np.nan)
     ctx.run(ref, q, k, v, mattn.Config(tokens, heads, heads, 128), kernel=_lib.KERNEL_SCALAR)
@@ -125,10 +130,14 @@ def test_key_mask(ctx, oracle, tokens, masked):
     for a, b in masked:
         mask[a:b] = -np.inf
     want = oracle.sdpa(q, k, v, heads, key_mask=mask)
-    for kernel in (_lib.KERNEL_TCGEN05, _lib.KERNEL_SCALAR):
+    results = {}
+    for kernel in (_lib.KERNEL_TCGEN05, _lib.KERNEL_SCALAR, _lib.KERNEL_TWO_TILE, _lib.KERNEL_ONE_TILE):
         got = np.full_like(q, np.nan)
         ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128), key_mask=mask, kernel=kernel)
         assert np.abs(got - want).max() <= 2e-3, f"kernel {kernel}"
+        results[kernel] = got
+    np.testing.assert_array_equal(results[_lib.KERNEL_TWO_TILE], results[_lib.KERNEL_ONE_TILE])
+    np.testing.assert_array_equal(results[_lib.KERNEL_TCGEN05], results[_lib.KERNEL_ONE_TILE])
 
 
 def test_finite_additive_mask_and_fully_masked(ctx, oracle):
@@ -137,18 +146,21 @@ def test_finite_additive_mask_and_fully_masked(ctx, oracle):
     q, k, v = (rng.standard_normal((tokens, heads, 128)).astype(np.float32) * 0.5 for _ in range(3))
     mask = rng.uniform(-2.0, 0.0, tokens).astype(np.float32)
     want = oracle.sdpa(q, k, v, heads, key_mask=mask)
-    got = np.full_like(q, np.nan)
-    ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128), key_mask=mask)
-    assert np.abs(got - want).max() <= 2e-3
-    # Every key masked: rows are written as zeros (the reference's math would give NaN).
-    got = np.full_like(q, np.nan)
-    ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128), key_mask=np.full(tokens, -np.inf, np.float32))
-    assert not got.any()
+    for form in (_lib.KERNEL_TWO_TILE, _lib.KERNEL_ONE_TILE):
+        got = np.full_like(q, np.nan)
+        ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128), key_mask=mask, kernel=form)
+        assert np.abs(got - want).max() <= 2e-3
+        # Every key masked: rows are written as zeros (the reference's math would give NaN).
+        got = np.full_like(q, np.nan)
+        ctx.run(got, q, k, v, mattn.Config(tokens, heads, heads, 128), key_mask=np.full(tokens, -np.inf, np.float32),
+                kernel=form)
+        assert not got.any()
 
 
+@pytest.mark.parametrize("form", [2, 3])  # the two-tile and the one-tile form of the kernel, pinned
 @pytest.mark.parametrize("out_layout", [0, 1])
 @pytest.mark.parametrize("qk_layout", [0, 1])
-def test_device_call_layouts_and_strides(ctx, oracle, out_layout, qk_layout):
+def test_device_call_layouts_and_strides(ctx, oracle, out_layout, qk_layout, form):
     """run_on_handles: both q/k layouts, both O layouts, a wide O row stride, batch of 2, f16 out."""
     batch, tokens, heads = 2, 200, 3
     rng = np.random.default_rng(11)
@@ -164,7 +176,7 @@ def test_device_call_layouts_and_strides(ctx, oracle, out_layout, qk_layout):
     else:
         to = torch.full((batch, heads, tokens, 128), float("nan"), dtype=torch.float16, device=dev)
     p = _lib.AttnParams(batch=batch, tokens=tokens, heads=heads, head_dim=128, in_dtype=1, out_dtype=1,
-                        out_layout=out_layout, qk_layout=qk_layout, ld_o=ld_o)
+                        out_layout=out_layout, qk_layout=qk_layout, ld_o=ld_o, kernel=form)
     ctx.run_on_handles(tq, tk, tv, to, p)
     torch.cuda.synchronize()
     assert ctx.last_status() == 0

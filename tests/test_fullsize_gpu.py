@@ -122,6 +122,25 @@ def test_head_shard_equals_full_run(ctx, name, h0, h1):
     assert torch.isnan(out[:, :, :h0].float()).all() and torch.isnan(out[:, :, h1:].float()).all()
 
 
+def test_one_tile_form_over_several_waves_equals_two_tile_form(ctx):
+    """The one-tile form pinned on a call with more query tiles than SMs (klein_1024 on 8 heads: 288 tiles,
+    two waves of CTAs) gives the bytes of the two-tile form."""
+    w = workloads.WORKLOADS["klein_1024"]
+    x = workloads.make_inputs(w, "cuda")
+    ld = w.heads * 128
+    xs = dict(x)
+    for n in ("q", "k", "v"):
+        xs[n] = x[n][:, :, 4:12]
+    outs = []
+    for form in (_lib.KERNEL_TWO_TILE, _lib.KERNEL_ONE_TILE):
+        out = torch.empty((1, w.tokens, 8, 128), dtype=torch.float16, device="cuda")
+        out.view(torch.uint8).fill_(0xFF)
+        run_joint(ctx, w, xs, p=workloads.params(w, heads=8, ld_q=ld, ld_k=ld, ld_v=ld, kernel=form), out=out)
+        outs.append(out)
+    assert not torch.isnan(outs[0].float()).any()
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+
+
 def test_properties_constant_v_and_key_permutation(ctx):
     w = workloads.WORKLOADS["klein_1024"]
     x = workloads.make_inputs(w, "cuda")

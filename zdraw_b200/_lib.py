@@ -17,7 +17,7 @@ CSRC_DIR = os.path.join(_HERE, "csrc")
 OK, DECLINED, E_ARG, E_CUDA, E_DEVICE = 0, 1, -1, -2, -3
 DTYPE_F16, DTYPE_F32 = 1, 3
 LAYOUT_TOKEN_MAJOR, LAYOUT_HEAD_MAJOR = 0, 1
-KERNEL_TCGEN05, KERNEL_SCALAR = 0, 1
+KERNEL_TCGEN05, KERNEL_SCALAR, KERNEL_TWO_TILE, KERNEL_ONE_TILE = 0, 1, 2, 3
 HEAD_DIM = 128
 
 

@@ -62,7 +62,7 @@ int validate(Ctx* c, const zdraw_cuda_attn_params* p, Shape* s) {
     return fail(c, ZDRAW_CUDA_E_ARG, "in_dtype %u is not f16/f32", p->in_dtype);
   if (p->out_dtype != ZDRAW_DTYPE_F16 && p->out_dtype != ZDRAW_DTYPE_F32)
     return fail(c, ZDRAW_CUDA_E_ARG, "out_dtype %u is not f16/f32", p->out_dtype);
-  if (p->out_layout > 1 || p->qk_layout > 1 || p->has_key_mask > 1 || p->kernel > 1)
+  if (p->out_layout > 1 || p->qk_layout > 1 || p->has_key_mask > 1 || p->kernel > ZDRAW_KERNEL_TCGEN05_ONE_TILE)
     return fail(c, ZDRAW_CUDA_E_ARG, "bad layout/flag/kernel code");
   if (p->txt_tokens > p->tokens) return fail(c, ZDRAW_CUDA_E_ARG, "txt_tokens > tokens");
   if (!(p->softmax_scale >= 0.0f) || std::isinf(p->softmax_scale))
@@ -290,7 +290,8 @@ int run_attention(Ctx* c, cudaStream_t stream, const void* q16, const void* k16,
   }
   a.status = c->d_status;
   a.trace = c->d_trace;
-  ZD_CUDA(c, zdraw::launch_attn_fwd(stream, tm_q, tm_k, tm_v, tm_o, a, c->sm_count));
+  const int form = p->kernel == ZDRAW_KERNEL_TCGEN05_TWO_TILE ? 2 : (p->kernel == ZDRAW_KERNEL_TCGEN05_ONE_TILE ? 1 : 0);
+  ZD_CUDA(c, zdraw::launch_attn_fwd(stream, tm_q, tm_k, tm_v, tm_o, a, c->sm_count, form));
   return ZDRAW_CUDA_OK;
 }
 

@@ -1361,7 +1361,8 @@ bool attn_fwd_takes_steps_kernel(int tokens, int heads, int batch, int sm_count,
 }
 
 cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
-                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args, int sm_count) {
+                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args, int sm_count,
+                            int form) {
   const int n_q_tiles = (args.tokens + kBM - 1) / kBM;
   // Programmatic dependent launch: the kernel may become resident while the preceding kernel in
   // the stream drains; it calls griddepcontrol.wait before touching that kernel's results.
@@ -1373,7 +1374,10 @@ cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (attn_fwd_takes_steps_kernel(args.tokens, args.heads, args.batch, sm_count, args.trace != nullptr)) {
+  const bool traced = args.trace != nullptr;
+  const bool one_tile = form == 0 ? attn_fwd_takes_steps_kernel(args.tokens, args.heads, args.batch, sm_count, traced)
+                                  : (form == 1 && !traced);
+  if (one_tile) {
     cfg.gridDim = dim3(n_q_tiles, args.heads, args.batch);
     cfg.dynamicSmemBytes = kS1SmemBytes;
     return cudaLaunchKernelEx(&cfg, attn_fwd_steps_kernel, tm_q, tm_k, tm_v, tm_o, args);

@@ -66,8 +66,11 @@ int attn_fwd_trace_words();
 cudaError_t attn_fwd_configure();  // raises the kernel's dynamic shared-memory limit (once per device)
 // sm_count: SMs of the device (0 = unknown). A call with at most one query tile per SM runs on the
 // one-tile kernel that interleaves the K/V steps of a tile; both kernels give the same bytes.
+// form: 0 = that rule, 1 = the one-tile kernel whatever the size, 2 = the two-tile kernel (a
+// traced launch always takes the two-tile kernel, which carries the time stamps).
 cudaError_t launch_attn_fwd(cudaStream_t stream, const CUtensorMap& tm_q, const CUtensorMap& tm_k,
-                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args, int sm_count);
+                            const CUtensorMap& tm_v, const CUtensorMap& tm_o, const AttnArgs& args, int sm_count,
+                            int form = 0);
 bool attn_fwd_takes_steps_kernel(int tokens, int heads, int batch, int sm_count, bool traced);
 cudaError_t launch_attn_scalar(cudaStream_t stream, const ScalarArgs& args);
 // Self-test: one small CTA whose bounded waits run out after limit_ns and set bit 8 of *status.
