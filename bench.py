@@ -523,6 +523,31 @@ def main():
     ms_prologue = timed(prologue)
     ms_attention = timed(attention)
 
+    # ---- the other attention shape next to the path: one head of 512 channels over 16384 tokens
+    #      (VAE mid-block at 1024 px), built from the projection kernel and a row softmax; timed before the
+    #      projection section, whose seconds of dense GEMMs leave the board at its sustained clocks
+    #      (the same 20 calls then take 0.77 ms instead of 0.66-0.70)
+    wide = None
+    if not by_heads:
+        wt, wd = 16384, 512
+        g = torch.Generator(device="cuda").manual_seed(w.seed + 11)
+        wq, wk, wv = (torch.randn((wt, wd), device="cuda", generator=g) for _ in range(3))
+        wo = torch.empty((wt, wd), device="cuda")
+        wcfg = mattn.Config(wt, 1, 1, wd)
+
+        def wide_step(i):
+            ctx.wide_attention(wq, wk, wv, wo, wcfg, stream=stream)
+
+        ms_w = timed(wide_step)
+        wide = {"api": "zdraw_cuda_wide_attention", "tokens": wt, "head_dim": wd, "ms_per_call": ms_w,
+                "achieved": 4.0 * wt * wt * wd / ms_w / 1e9, "unit": "TFLOP/s",
+                "kernels": "2 casts (half + e4m3), transpose, linear_kernel x3 (row max of S on e4m3 operands; "
+                           "exp(S - max) in half + row sums; P V / row sum), row_sum_inverse_kernel",
+                "l2": "exp(scores) in half (0.5 GB) streams through HBM once each way"}
+        del wq, wk, wv, wo
+        if ctx.last_status() != 0:
+            raise SystemExit("the wide attention reported a non-zero status")
+
     # ---- the projection GEMM either side of attention (Q projection with the prologue as its
     #      epilogue; a plain f16 projection such as V or the output projection), same token count
     projection = None
@@ -604,29 +629,6 @@ def main():
         del acts, wts, c_plain, c_qk
         if ctx.last_status() != 0:
             raise SystemExit("the projection kernel reported a non-zero status")
-
-    # ---- the other attention shape next to the path: one head of 512 channels over 16384 tokens
-    #      (VAE mid-block at 1024 px), built from the projection kernel and a row softmax
-    wide = None
-    if not by_heads:
-        wt, wd = 16384, 512
-        g = torch.Generator(device="cuda").manual_seed(w.seed + 11)
-        wq, wk, wv = (torch.randn((wt, wd), device="cuda", generator=g) for _ in range(3))
-        wo = torch.empty((wt, wd), device="cuda")
-        wcfg = mattn.Config(wt, 1, 1, wd)
-
-        def wide_step(i):
-            ctx.wide_attention(wq, wk, wv, wo, wcfg, stream=stream)
-
-        ms_w = timed(wide_step)
-        wide = {"api": "zdraw_cuda_wide_attention", "tokens": wt, "head_dim": wd, "ms_per_call": ms_w,
-                "achieved": 4.0 * wt * wt * wd / ms_w / 1e9, "unit": "TFLOP/s",
-                "kernels": "2 casts (half + e4m3), transpose, linear_kernel x3 (row max of S on e4m3 operands; "
-                           "exp(S - max) in half + row sums; P V / row sum), row_sum_inverse_kernel",
-                "l2": "exp(scores) in half (0.5 GB) streams through HBM once each way"}
-        del wq, wk, wv, wo
-        if ctx.last_status() != 0:
-            raise SystemExit("the wide attention reported a non-zero status")
 
     # ---- end to end from pinned host buffers through the host-buffer C-ABI entry point
     xh = workloads.make_inputs(w, "cpu", pin=True)
