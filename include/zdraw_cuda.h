@@ -57,7 +57,7 @@ extern "C" {
  * a slow scalar kernel kept to cross-check it in tests (the reference keeps `attention_rows`
  * beside its fast kernels the same way, src/metal/mattn_test.zig:91-128); 2 and 3 pin the form
  * of the tcgen05 kernel whatever the size of the call (tests compare the two forms; the
- * reference's env switches that pin a route, src/metal/mattn.zig:134-150, are the model). */
+ * reference's ZDRAW_ATTN / ZDRAW_ATTN_WIDE switches, src/metal/mattn.zig:22, 285-287, are the model). */
 #define ZDRAW_KERNEL_TCGEN05 0u
 #define ZDRAW_KERNEL_SCALAR 1u
 #define ZDRAW_KERNEL_TCGEN05_TWO_TILE 2u
