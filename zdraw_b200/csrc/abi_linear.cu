@@ -134,10 +134,10 @@ int run_linear(Ctx* cx, void* stream, const void* a, int n_parts, const PartSpec
     const bool f32 = p->c_dtype == ZDRAW_DTYPE_F32;
     const cuuint64_t dims[2] = {p->n, p->m};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_c) * (f32 ? 4u : 2u)};
-    const cuuint32_t box[2] = {32u, 32u};  // 128-byte rows of f32, 64-byte rows of f16
+    const cuuint32_t box[2] = {f32 ? 32u : 64u, 32u};  // 128-byte rows either way: 32 f32 or 64 f16 columns
     const cuuint32_t es[2] = {1, 1};
     if (cx->encode(&maps.c[i], f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, parts[i].c, dims,
-                   strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return fail(cx, ZDRAW_CUDA_E_CUDA, "cuTensorMapEncodeTiled failed for C");
   }

@@ -62,7 +62,7 @@ constexpr int kBarDrain = 2 * kStages + 4;     // [1]
 constexpr int kNumBars = 2 * kStages + 5;
 constexpr int kOffFlags = kOffBar + kNumBars * 8;
 // Per epilogue warp 8 KB: qk epilogue, 16 columns of 32 tokens' cos and sin rows (2 x 32 x 64
-// bytes, the first half); plain epilogue, four 2 KB blocks of 64-byte row pieces on their way
+// bytes, the first half); plain epilogue, two 4 KB blocks of 128-byte row pieces on their way
 // to a tile store (a store takes over a thousand clocks to read its block, so several must be
 // in flight per warp to drain a 128 x 256 f32 tile in the time the next tile's MMAs take).
 constexpr int kTabBytesPerWarp = 8192;
@@ -262,6 +262,7 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
       const uint32_t t_acc = tmem_base + 256u * b + lane_off;
       const long long m = static_cast<long long>(tile_m) * kTM + row;
       const bool live = m < a.m;
+      bool released = false;  // this warp has handed the accumulator back
 
       if (part.epilogue == kEpilogueRowMax) {
         // Row maximum of the tile's columns, nothing stored: each thread reduces its 128 columns.
@@ -285,8 +286,8 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
       } else if (part.epilogue == kEpiloguePlain || part.epilogue == kEpilogueExp) {
         // A thread holds consecutive columns of ITS row, and rows lie ld_c apart, so storing from
         // registers would touch 32 different lines per instruction. Instead the warp parks its
-        // 32 rows x 32 columns in shared memory in the tensor map's swizzle (128-byte rows of f32,
-        // 64-byte rows of f16) and one lane hands the block to TMA, which writes it as a tile (rows past m
+        // 32 rows x 32 columns (f32) or 32 rows x 64 columns (f16) in shared memory in the tensor map's
+        // 128-byte swizzle and one lane hands the block to TMA, which writes it as a tile (rows past m
         // are clipped by the tensor map). The blocks rotate, so the next piece is read from TMEM while
         // the previous ones are on their way out.
         const CUtensorMap* tm_c = &maps.c[col / tiles_n];
@@ -305,13 +306,12 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
         } else if (part.row_scale != nullptr && live) {
           mul = part.row_scale[m];
         }
+        if (part.c_f32) {
 #pragma unroll 1
-        for (int pc = 0; pc < 4; ++pc) {  // 32 columns of this warp's 128 at a time
-          uint32_t x[32];
-          tmem_ld_x32(t_acc + 128u * hh + 32u * pc, x);
-          tmem_wait_ld();
-          uint32_t src;
-          if (part.c_f32) {
+          for (int pc = 0; pc < 4; ++pc) {  // 32 columns of this warp's 128 at a time
+            uint32_t x[32];
+            tmem_ld_x32(t_acc + 128u * hh + 32u * pc, x);
+            tmem_wait_ld();
             // 128-byte rows, 128-byte swizzle, two 4 KB blocks
             const int buf = pc & 1;
             if (lane == 0) bulk_wait_group_read<1>();  // the store that last used this block has read it
@@ -322,30 +322,54 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
               st[lane * 8 + (i ^ (lane & 7))] =
                   make_uint4(__float_as_uint(__uint_as_float(x[4 * i]) * mul), __float_as_uint(__uint_as_float(x[4 * i + 1]) * mul),
                              __float_as_uint(__uint_as_float(x[4 * i + 2]) * mul), __float_as_uint(__uint_as_float(x[4 * i + 3]) * mul));
-            src = stage_addr + buf * 4096;
-          } else {
-            // 64-byte rows, 64-byte swizzle, four 2 KB blocks
-            const int buf = pc & 3;
-            if (lane == 0) bulk_wait_group_read<3>();
+            fence_proxy_async_smem();  // this thread's writes, for the TMA engine
             __syncwarp();
-            uint4* st = stage + buf * 128;
-            const int sw = (lane >> 1) & 3;
+            if (lane == 0 && row0 < a.m) {
+              tma_store_2d(tm_c, stage_addr + buf * 4096, col_base + 32 * pc, row0);
+              bulk_commit_group();
+            }
+          }
+        } else {
+          // f16: 128-byte rows of 64 columns, 128-byte swizzle, two 4 KB blocks = the warp's 32 rows x
+          // 128 columns. The stores of the tile before have had a whole tile's time to read the
+          // blocks; the four 32-column pieces are read from TMEM one ahead of the arithmetic, written
+          // to the blocks, and one fence later both blocks leave as one tile store each (half as many
+          // store requests as 64-byte rows, whole lines, one proxy fence per tile instead of four).
+          if (lane == 0) bulk_wait_group_read<0>();
+          __syncwarp();
+          uint32_t xa[32], xb[32];
+          tmem_ld_x32(t_acc + 128u * hh, xa);
+          auto piece = [&](int pc, const uint32_t* x) {
+            uint4* st = stage + (pc >> 1) * 256;
+            const int side = pc & 1;
             uint32_t h[16];
             if (exp_mode) {
+              // (the subtracted maximum may be an estimate, admitted only with a proven error bound:
+              // a score whose exponential would leave the half range means that bound was broken;
+              // the largest raw score is tracked for that check, one instruction per pair, and the
+              // conversion saturates at the largest finite half)
               const int n_live = part.n_valid - (col_base + 32 * pc);  // columns of this piece that exist
+              if (n_live >= 32) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                // (the subtracted maximum may be an estimate, admitted only with a proven error bound:
-                // a score whose exponential would leave the half range means that bound was broken;
-                // the largest raw score is tracked for that check, one instruction per pair)
-                float e0 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias)), kHalfMax);
-                float e1 = fminf(ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias)), kHalfMax);
-                if (2 * i >= n_live) e0 = 0.0f;
-                if (2 * i + 1 >= n_live) e1 = 0.0f;
-                if (2 * i + 1 < n_live) top = max3(top, __uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
-                psum += e0 + e1;  // f32 sum of the unrounded values, as the reference's softmax takes it
-                const __half2 v = __floats2half2_rn(e0, e1);
-                h[i] = *reinterpret_cast<const uint32_t*>(&v);
+                for (int i = 0; i < 16; ++i) {
+                  const float e0 = ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias));
+                  const float e1 = ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias));
+                  top = max3(top, __uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
+                  psum += e0 + e1;  // f32 sum of the unrounded values, as the reference's softmax takes it
+                  h[i] = pack_f16x2_sat(e0, e1);
+                }
+              } else {  // the ragged end of the row (at most once per row)
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  float e0 = ex2_approx(fmaf(__uint_as_float(x[2 * i]), mul, bias));
+                  float e1 = ex2_approx(fmaf(__uint_as_float(x[2 * i + 1]), mul, bias));
+                  if (2 * i >= n_live) e0 = 0.0f;
+                  if (2 * i + 1 >= n_live) e1 = 0.0f;
+                  if (2 * i < n_live) top = fmaxf(top, __uint_as_float(x[2 * i]));
+                  if (2 * i + 1 < n_live) top = fmaxf(top, __uint_as_float(x[2 * i + 1]));
+                  psum += e0 + e1;
+                  h[i] = pack_f16x2_sat(e0, e1);
+                }
               }
             } else {
 #pragma unroll
@@ -353,13 +377,30 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
                 h[i] = pack_clamped(__uint_as_float(x[2 * i]) * mul, __uint_as_float(x[2 * i + 1]) * mul);
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i) st[lane * 4 + (i ^ sw)] = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
-            src = stage_addr + buf * 2048;
-          }
+            for (int i = 0; i < 4; ++i)
+              st[lane * 8 + ((4 * side + i) ^ (lane & 7))] = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+          };
+          tmem_wait_ld();
+          tmem_ld_x32(t_acc + 128u * hh + 32u, xb);
+          piece(0, xa);
+          tmem_wait_ld();
+          tmem_ld_x32(t_acc + 128u * hh + 64u, xa);
+          piece(1, xb);
+          tmem_wait_ld();
+          tmem_ld_x32(t_acc + 128u * hh + 96u, xb);
+          piece(2, xa);
+          tmem_wait_ld();
+          // The accumulator is in registers: the MMAs of the tile after next may have it now.
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(cluster_map(bar(kBarAccEmpty + b), 0));
+          released = true;
+          piece(3, xb);
           fence_proxy_async_smem();  // this thread's writes, for the TMA engine
           __syncwarp();
           if (lane == 0 && row0 < a.m) {
-            tma_store_2d(tm_c, src, col_base + 32 * pc, row0);
+            tma_store_2d(tm_c, stage_addr, col_base, row0);
+            tma_store_2d(tm_c, stage_addr + 4096, col_base + 64, row0);
             bulk_commit_group();
           }
         }
@@ -459,10 +500,12 @@ linear_kernel(const __grid_constant__ LinearMaps maps, const LinearArgs a) {
         }
       }
       // This accumulator may be overwritten by the tile after next, once every epilogue warp of
-      // the pair has said so to the even CTA.
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(cluster_map(bar(kBarAccEmpty + b), 0));
+      // the pair has said so to the even CTA (the f16 store path has said so already).
+      if (!released) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(cluster_map(bar(kBarAccEmpty + b), 0));
+      }
     }
     if (lane == 0) bulk_wait_group<0>();  // tile stores still in flight read this CTA's shared memory
     __syncwarp();
