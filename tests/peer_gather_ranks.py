@@ -4,6 +4,11 @@ Heads of one image are split over the ranks; every rank's attention epilogue sto
 ranks' gathered buffers; the fence kernel after it adds 1 to every rank's arrival counter and polls its own
 (bounded), after which a rank must hold the bytes of a 1-GPU run of the whole call. Steps use different inputs and alternate the
 two gathered buffers. Prints "PEER_GATHER_OK <rank>" on success.
+
+With a second argument "missing" one more step follows in which the last rank never signals (a
+failure made on the host: it simply does not enqueue its fence): the other ranks' bounded polls run
+out after 20 ms and set bit 9 of their status words, nothing hangs or faults, and every rank prints
+"PEER_GATHER_MISSING_OK <rank> <status>".
 """
 import os
 import sys
@@ -57,6 +62,19 @@ def main():
             torch.cuda.synchronize()
             assert torch.equal(got.view(torch.int16), full.view(torch.int16)), "gathered bytes differ from the 1-GPU run"
         print(f"PEER_GATHER_OK {rank}", flush=True)
+        if len(sys.argv) > 2 and sys.argv[2] == "missing":
+            _, x = steps[0]
+            pg.begin_step(hs.begin)
+            ctx.joint_attention(x["q"][:, :, hsl], x["k"][:, :, hsl], x["v"][:, :, hsl], x["q_w_txt"], x["q_w_img"],
+                                x["k_w_txt"], x["k_w_img"], x["rope_cos"], x["rope_sin"], mine, p_shard)
+            if rank != world - 1:
+                pg.fence(limit_ns=20_000_000)  # the last rank's addition never comes
+            torch.cuda.synchronize()
+            status = ctx.last_status()  # read (and cleared) on the host, as after any give-up
+            assert status == (0x200 if rank != world - 1 else 0), hex(status)
+            assert ctx.last_status() == 0
+            ctx.set_gather(None)
+            print(f"PEER_GATHER_MISSING_OK {rank} {status:#x}", flush=True)
     finally:
         if pg is not None:
             pg.close()
